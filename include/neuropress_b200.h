@@ -1,0 +1,152 @@
+/*
+ * neuropress_b200.h — C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, never allocates, never synchronises, and returns an
+ * npb_status.  The caller owns every buffer (inputs, outputs, scratch).  Pointers are
+ * device pointers unless stated otherwise.
+ *
+ * Weight formats (identical to the reference's wire formats):
+ *   - VQ index stream: 1-D uint8, LSB-first bit-stream, index i occupies bits
+ *     [i*bits, (i+1)*bits); flat order n*G + g with G = K / vector_len
+ *     (neuropress/transforms/vq_packing.py:210-252, IndexPacking._pack_bitstream).
+ *   - Codebook: fp16 [num_centroids, vector_len] (neuropress/nn/np_vq_linear.py:421-427).
+ *   - Group-affine codes: uint8 [N, K*nbits/8], value j of a byte at bits
+ *     [j*nbits, (j+1)*nbits) (neuropress/nn/np_linear.py:78-117), fp16 scale / zero-point
+ *     flat [N * K/group_size].
+ */
+#ifndef NEUROPRESS_B200_H_
+#define NEUROPRESS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque CUDA stream handle (a cudaStream_t / CUstream passed as a pointer). */
+typedef void* npb_stream_t;
+
+typedef enum {
+  NPB_OK = 0,
+  NPB_ERR_INVALID_ARG = 1,     /* null pointer, negative size, bad enum          */
+  NPB_ERR_UNSUPPORTED = 2,     /* bits / vector_len / dtype / shape not handled  */
+  NPB_ERR_SHAPE = 3,           /* K % vector_len, packed buffer too short, ...   */
+  NPB_ERR_ALIGNMENT = 4,       /* pointer not aligned as the kernel requires     */
+  NPB_ERR_CUDA = 5,            /* a CUDA runtime / driver call failed            */
+  NPB_ERR_TOO_LARGE = 6,       /* exceeds a fixed capacity (no-alloc entry point)*/
+  NPB_ERR_DEVICE_TIMEOUT = 7   /* a bounded in-kernel wait gave up               */
+} npb_status;
+
+typedef enum { NPB_F16 = 0, NPB_BF16 = 1, NPB_F32 = 2 } npb_dtype;
+
+/* Largest row count the fused GEMV kernels accept (the decode band is 1-2 rows by
+ * default; up to this many rows are supported for tuning the band edge). */
+#define NPB_GEMV_MAX_ROWS 8
+
+/*
+ * One vector-quantized weight matrix W[N, K].
+ *   W16[n, VL*g + j] = hmul(hadd(C[cb(g)][idx[n,g]][j], R[ridx[n,g]][j]), s[n])   (fp16, RN)
+ * with the residual term and the row scale optional, cb(g) = (g*VL) / cols_per_codebook.
+ * Without residual / scale this is exactly the reference decode
+ * (neuropress/kernels/vq_dequant.cu:1-18, neuropress/nn/np_vq_linear.py:1091-1095).
+ */
+typedef struct {
+  const uint8_t* packed;        /* main index stream                                  */
+  int64_t packed_bytes;
+  int32_t bits;                 /* 4..16                                              */
+  int32_t vector_len;           /* 4 or 8                                             */
+  const void* centroids;        /* fp16 [n_codebooks * num_centroids, vector_len]     */
+  int32_t num_centroids;        /* entries per codebook                               */
+  int32_t cols_per_codebook;    /* 0: one codebook for all columns                    */
+  const uint8_t* res_packed;    /* residual index stream or NULL                      */
+  int64_t res_packed_bytes;
+  int32_t res_bits;
+  int32_t res_num_centroids;
+  const void* res_centroids;    /* fp16 [res_num_centroids, vector_len] or NULL       */
+  const void* row_scale;        /* fp16 [N] or NULL                                   */
+} npb_vq_weight;
+
+/*
+ * One group-affine weight matrix W[N, K] = (q - zp) * scale, fp32 arithmetic, cast to the
+ * activation dtype (neuropress/nn/np_linear.py:298-353; kernel q4_linear.cu:80-131).
+ * zero_point == NULL means the symmetric scheme with zp = 2^(nbits-1).
+ */
+typedef struct {
+  const uint8_t* codes;         /* uint8 [N, K*nbits/8]                               */
+  const void* scale;            /* fp16 [N * K/group_size]                            */
+  const void* zero_point;       /* fp16 [N * K/group_size] or NULL                    */
+  int32_t nbits;                /* 4 (8 also accepted by decode / GEMV)               */
+  int32_t group_size;           /* multiple of 8, divides K                           */
+} npb_q_weight;
+
+const char* npb_status_string(int status);
+/* Text of the most recent CUDA error seen by this library on the calling thread. */
+const char* npb_last_cuda_error(void);
+int npb_version(void);
+
+/* ---- one-pass decode (large-batch band, and the bit-exact parity anchor) ---------- */
+
+/* out[N, K] in out_dtype.  Replaces vq_dequant (neuropress/kernels/vq_dequant.cu:105-146;
+ * Python wrapper neuropress/kernels/__init__.py:497-529). */
+int npb_vq_decode(const npb_vq_weight* w, int64_t N, int64_t K, void* out, int out_dtype,
+                  npb_stream_t stream);
+
+/* out[N, K] in out_dtype.  GPU form of the dequantisation inside _q_dequant_linear
+ * (neuropress/nn/np_linear.py:334-351). */
+int npb_q_decode(const npb_q_weight* w, int64_t N, int64_t K, void* out, int out_dtype,
+                 npb_stream_t stream);
+
+/* ---- fused index-decode GEMV (1..NPB_GEMV_MAX_ROWS rows) --------------------------- */
+
+/* y[M, N] = x[M, K] . W^T (+ bias), x / y in x_dtype, bias fp32 [N] or NULL.
+ * Replaces vq_linear / vq_linear_wmma's GEMV branch / vq_lut_gather
+ * (neuropress/kernels/vq_linear.cu:344-424, vq_linear_wmma.cu:187-240,468-540,
+ * vq_linear_lut.cu:121-206). */
+int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+                int64_t K, const float* bias, void* y, npb_stream_t stream);
+
+/* Same contract for group-affine weights.  Replaces q_linear
+ * (neuropress/kernels/q4_linear.cu:179-253). */
+int npb_q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+               int64_t K, const float* bias, void* y, npb_stream_t stream);
+
+/* ---- tensor-core GEMMs (tcgen05 / TMEM) --------------------------------------------- */
+
+/* y[M, N] = x[M, K] . w[N, K]^T (+ bias); x, w, y in dtype (NPB_BF16 or NPB_F16), fp32
+ * accumulation, bias fp32 [N] or NULL.  Stands in for the cuBLAS call after the decode
+ * (F.linear at neuropress/nn/np_vq_linear.py:1148).  K % 8 == 0 and 16-byte aligned
+ * pointers are required (TMA). */
+int npb_gemm(const void* x, const void* w, const float* bias, void* y, int64_t M, int64_t N,
+             int64_t K, int dtype, npb_stream_t stream);
+
+/* Tile-decode GEMM: B tiles are decoded from the index stream straight into the swizzled
+ * shared-memory stage, never written to HBM.  Replaces vq_gemm_triton
+ * (neuropress/kernels/vq_triton.py:37-179) and vq_linear_wmma's GEMM branch
+ * (vq_linear_wmma.cu:261-394).  vector_len 8, K % 64 == 0. */
+int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
+                      int64_t N, int64_t K, const float* bias, void* y, npb_stream_t stream);
+
+/* Same for group-affine weights (no reference counterpart beyond q_linear, which re-reads
+ * the weight per row: neuropress/kernels/q4_linear.cu:80-131). nbits 4, K % 64 == 0. */
+int npb_q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+                     int64_t K, const float* bias, void* y, npb_stream_t stream);
+
+/* Test hook, no reference counterpart: runs the tile decoder of npb_vq_gemm_fused on one
+ * 128-row x 64-column W tile (rows [128*tile_n, +128), columns [64*k_block, +64)) and writes
+ * the 16 KiB shared-memory image to out: row r occupies bytes [128 r, 128 r + 128), its
+ * 16-byte chunk c is stored at chunk position c ^ (r & 7) (the 128-byte swizzle the tensor
+ * core reads); rows past N are zero.  dtype NPB_BF16 or NPB_F16. */
+int npb_test_vq_decode_tile(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
+                            int dtype, void* out, npb_stream_t stream);
+
+/* Every wait inside the tensor-core GEMMs (on an mbarrier) is bounded; a kernel that gives up
+ * records which role did so, frees its tensor memory and returns.  This call synchronises the
+ * device, copies that record to *host_out (0 = no give-up since the last call), clears it, and
+ * returns NPB_ERR_DEVICE_TIMEOUT if it was set.  No reference counterpart. */
+int npb_gemm_device_status(int* host_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEUROPRESS_B200_H_ */

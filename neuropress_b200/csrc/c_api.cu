@@ -1,0 +1,166 @@
+// extern "C" surface of libneuropress_b200.so: argument validation, status strings and the
+// thin forwarding layer onto the kernels.  No torch types, no allocation, no host sync.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace npb {
+
+// kernels (one translation unit each)
+int vq_decode(const npb_vq_weight*, int64_t, int64_t, void*, int, cudaStream_t);
+int vq_gemv(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
+            void*, cudaStream_t);
+int q_decode(const npb_q_weight*, int64_t, int64_t, void*, int, cudaStream_t);
+int q_gemv(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
+           cudaStream_t);
+int gemm(const void*, const void*, const float*, void*, int64_t, int64_t, int64_t, int,
+         cudaStream_t);
+int vq_gemm_fused(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t,
+                  const float*, void*, cudaStream_t);
+int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
+                 void*, cudaStream_t);
+
+int gemm_device_status(int*);
+int vq_decode_tile_probe(const npb_vq_weight*, int64_t, int64_t, int, int, int, void*, cudaStream_t);
+
+static thread_local char g_last_error[256] = "";
+
+void set_last_cuda_error(cudaError_t e, const char* where) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorName(e),
+           cudaGetErrorString(e));
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int max_dynamic_smem() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 48 * 1024;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+        n <= 0)
+      n = 48 * 1024;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int validate_vq(const npb_vq_weight* w, int64_t N, int64_t K) {
+  if (w == nullptr || N < 0 || K < 0) return NPB_ERR_INVALID_ARG;
+  if (w->vector_len != 4 && w->vector_len != 8) return NPB_ERR_UNSUPPORTED;
+  if (w->bits < 4 || w->bits > 16) return NPB_ERR_UNSUPPORTED;
+  if (K % w->vector_len != 0) return NPB_ERR_SHAPE;
+  const int64_t n_vectors = N * (K / w->vector_len);
+  if (n_vectors == 0) return NPB_OK;
+  if (w->packed == nullptr || w->centroids == nullptr) return NPB_ERR_INVALID_ARG;
+  if (w->num_centroids <= 0 || w->num_centroids > (1 << w->bits)) {
+    // A codebook larger than the index range is legal (unused rows); smaller than 1 is not.
+    if (w->num_centroids <= 0) return NPB_ERR_INVALID_ARG;
+  }
+  if ((n_vectors * w->bits + 7) / 8 > w->packed_bytes) return NPB_ERR_SHAPE;
+  if (w->cols_per_codebook < 0 || (w->cols_per_codebook % w->vector_len) != 0)
+    return NPB_ERR_SHAPE;
+  if (w->res_packed != nullptr) {
+    if (w->res_centroids == nullptr || w->res_num_centroids <= 0) return NPB_ERR_INVALID_ARG;
+    if (w->res_bits < 4 || w->res_bits > 16) return NPB_ERR_UNSUPPORTED;
+    if ((n_vectors * w->res_bits + 7) / 8 > w->res_packed_bytes) return NPB_ERR_SHAPE;
+  }
+  const size_t cb_align = (size_t)w->vector_len * 2;
+  if (!aligned_to(w->centroids, cb_align)) return NPB_ERR_ALIGNMENT;
+  if (w->res_centroids && !aligned_to(w->res_centroids, cb_align)) return NPB_ERR_ALIGNMENT;
+  if (w->row_scale && !aligned_to(w->row_scale, 2)) return NPB_ERR_ALIGNMENT;
+  return NPB_OK;
+}
+
+int validate_q(const npb_q_weight* w, int64_t N, int64_t K) {
+  if (w == nullptr || N < 0 || K < 0) return NPB_ERR_INVALID_ARG;
+  if (w->nbits != 4 && w->nbits != 8) return NPB_ERR_UNSUPPORTED;
+  if (w->group_size <= 0 || w->group_size % 8 != 0) return NPB_ERR_UNSUPPORTED;
+  if (K % w->group_size != 0) return NPB_ERR_SHAPE;
+  if (N * K == 0) return NPB_OK;
+  if (w->codes == nullptr || w->scale == nullptr) return NPB_ERR_INVALID_ARG;
+  if (!aligned_to(w->scale, 2) || (w->zero_point && !aligned_to(w->zero_point, 2)))
+    return NPB_ERR_ALIGNMENT;
+  if (!aligned_to(w->codes, 4)) return NPB_ERR_ALIGNMENT;
+  return NPB_OK;
+}
+
+}  // namespace npb
+
+extern "C" {
+
+const char* npb_status_string(int status) {
+  switch (status) {
+    case NPB_OK: return "ok";
+    case NPB_ERR_INVALID_ARG: return "invalid argument (null pointer, negative size or bad enum)";
+    case NPB_ERR_UNSUPPORTED: return "unsupported bits / vector_len / dtype / shape";
+    case NPB_ERR_SHAPE: return "inconsistent shape (K % vector_len, group size, or packed buffer too short)";
+    case NPB_ERR_ALIGNMENT: return "pointer not aligned as required";
+    case NPB_ERR_CUDA: return "CUDA call failed (see npb_last_cuda_error)";
+    case NPB_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
+    case NPB_ERR_DEVICE_TIMEOUT: return "a bounded in-kernel wait gave up";
+    default: return "unknown status";
+  }
+}
+
+const char* npb_last_cuda_error(void) { return npb::g_last_error; }
+
+int npb_version(void) { return 100; }
+
+int npb_vq_decode(const npb_vq_weight* w, int64_t N, int64_t K, void* out, int out_dtype,
+                  npb_stream_t stream) {
+  return npb::vq_decode(w, N, K, out, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int npb_q_decode(const npb_q_weight* w, int64_t N, int64_t K, void* out, int out_dtype,
+                 npb_stream_t stream) {
+  return npb::q_decode(w, N, K, out, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+                int64_t K, const float* bias, void* y, npb_stream_t stream) {
+  return npb::vq_gemv(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+}
+
+int npb_q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+               int64_t K, const float* bias, void* y, npb_stream_t stream) {
+  return npb::q_gemv(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+}
+
+int npb_gemm(const void* x, const void* w, const float* bias, void* y, int64_t M, int64_t N,
+             int64_t K, int dtype, npb_stream_t stream) {
+  return npb::gemm(x, w, bias, y, M, N, K, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
+                      int64_t N, int64_t K, const float* bias, void* y, npb_stream_t stream) {
+  return npb::vq_gemm_fused(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+}
+
+int npb_q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+                     int64_t K, const float* bias, void* y, npb_stream_t stream) {
+  return npb::q_gemm_fused(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+}
+
+int npb_test_vq_decode_tile(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
+                            int dtype, void* out, npb_stream_t stream) {
+  return npb::vq_decode_tile_probe(w, N, K, tile_n, k_block, dtype, out,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }
+
+}  // extern "C"

@@ -1,0 +1,714 @@
+// Persistent warp-specialised tcgen05 GEMM  y[M,N] = x[M,K] . W[N,K]^T (+ bias)  for sm_100a,
+// in three flavours selected at compile time by where the W tile comes from:
+//
+//   B_TMA : W is a dense [N,K] matrix in HBM (the large-batch band after the one-pass decode);
+//           W tiles arrive by TMA like the x tiles.
+//   B_VQ  : W tiles are decoded from the packed index stream + codebook(s) by four decode
+//           warps straight into the 128B-swizzled shared-memory stage (mid-batch band; the
+//           dense weight never exists in HBM).  One 16-byte centroid (VL = 8) is exactly one
+//           swizzle chunk, so a decoded vector is a single st.shared.v4.
+//   B_Q4  : same, W tiles dequantised from 4-bit group-affine codes.
+//
+// CTA = 128 x (MT*128 rows) x BN tile, K step 64.  Warp roles: warp 0 TMA producer, warp 1
+// TMEM owner + single-thread tcgen05.mma issuer, warps 2-5 epilogue (tcgen05.ld -> bias ->
+// T -> global), warps 6-9 (fused modes) B decoders.  smem ring of STAGES stages guarded by
+// full/empty mbarriers; accumulators live in TMEM (MT*BN fp32 columns per buffer, two buffers
+// when they fit so the epilogue of tile i overlaps the MMAs of tile i+1).  Every mbarrier wait
+// is bounded: on give-up the CTA raises an abort flag, records it in g_gemm_status, lets the
+// outstanding copies land, frees its TMEM and returns.
+//
+// Bounds: fp32 accumulate of bf16/fp16 products; tensor-pipe bound for M >= ~1024, decode /
+// L2-gather bound in the fused modes.  FLOPs = 2*M*N*K; HBM bytes = operands once (x tiles are
+// re-read from L2).
+//
+// Stands in for: cuBLAS via F.linear (neuropress/nn/np_vq_linear.py:1148), the Triton
+// tile-decode GEMM (neuropress/kernels/vq_triton.py:37-116) and the wmma GEMM
+// (neuropress/kernels/vq_linear_wmma.cu:261-394).
+#include <type_traits>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace npb {
+
+__device__ int g_gemm_status = 0;  // 0 ok; 1..4: the role whose wait gave up; >= 10: a
+                                   // decoder refused an out-of-range access (see below)
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK = 64;            // 64 x 16-bit = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kAStageBytes = BM * BK * 2;                 // 16 KiB per 128-row A sub-tile
+constexpr uint64_t kWaitTimeoutNs = 2000000000ull;        // 2 s
+
+enum BMode { B_TMA = 0, B_VQ = 1, B_Q4 = 2 };
+
+struct FusedVq {
+  const uint8_t* packed;
+  int64_t packed_bytes;
+  const __half* centroids;
+  const uint8_t* res_packed;
+  int64_t res_bytes;
+  const __half* res_centroids;
+  const __half* row_scale;
+  int bits, res_bits, num_centroids, groups_per_codebook;
+  int cb_rows, res_rows;  // total codebook rows (n_codebooks * num_centroids), residual rows
+};
+
+struct FusedQ4 {
+  const uint8_t* codes;
+  const __half* scale;
+  const __half* zp;
+  int group_size;
+};
+
+struct GemmParams {
+  const float* bias;
+  void* y;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  FusedVq vq;
+  FusedQ4 q4;
+};
+
+template <int BN, int MT>
+struct SmemLayout {
+  static constexpr int kStageBytes = MT * kAStageBytes + BN * BK * 2;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int stages(int smem_cap) {
+    int s = (smem_cap - kBarrierBytes - 1024 /*alignment slack*/) / kStageBytes;
+    return s > 8 ? 8 : s;
+  }
+};
+
+// ---- B tile decoders (fused modes) ---------------------------------------------------------
+// One decode thread owns one W row of the tile (BN == 128 == decode threads) and writes its
+// eight 16-byte chunks of the current 64-wide K block.
+template <typename T>
+__device__ __forceinline__ uint4 pack_half8(const __half2 (&h)[4]) {
+  if constexpr (sizeof(T) == 2 && !std::is_same<T, __nv_bfloat16>::value) {
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&h[0]);
+    o.y = *reinterpret_cast<const uint32_t*>(&h[1]);
+    o.z = *reinterpret_cast<const uint32_t*>(&h[2]);
+    o.w = *reinterpret_cast<const uint32_t*>(&h[3]);
+    return o;
+  } else {
+    __nv_bfloat162 b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      b[i] = __floats2bfloat162_rn(f.x, f.y);  // same rounding as from_half<bf16>
+    }
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&b[0]);
+    o.y = *reinterpret_cast<const uint32_t*>(&b[1]);
+    o.z = *reinterpret_cast<const uint32_t*>(&b[2]);
+    o.w = *reinterpret_cast<const uint32_t*>(&b[3]);
+    return o;
+  }
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <typename T, int BITS>
+__device__ __forceinline__ void decode_vq_row(const FusedVq& p, int n, int N, int G, int kb,
+                                              uint32_t b_stage, int row) {
+  const uint32_t row_addr = b_stage + row * 128;
+  const int sw = row & 7;
+  if (n >= N) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) st_shared_v4(row_addr + ((c ^ sw) << 4), z);
+    return;
+  }
+  uint32_t idx[8], ridx[8];
+  const bool has_res = p.res_packed != nullptr;
+  if constexpr (BITS != 0) {
+    const int64_t chunk = (int64_t)n * (G >> 3) + kb;
+    // The decoder checks its own accesses: a stream offset or codebook index outside the
+    // buffers is recorded (status 10 / 11) and replaced by entry 0 instead of being read.
+    if ((chunk + 1) * BITS > p.packed_bytes || (has_res && (chunk + 1) * 8 > p.res_bytes)) {
+      atomicExch(&g_gemm_status, 10);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) { idx[c] = 0; ridx[c] = 0; }
+    } else {
+      read_index8<BITS>(p.packed, chunk, idx);
+      if (has_res) read_index8<8>(p.res_packed, chunk, ridx);
+    }
+  } else {
+    const int64_t v0 = (int64_t)n * G + kb * 8;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      idx[c] = read_index_generic(p.packed, p.packed_bytes, v0 + c, p.bits);
+      if (has_res) ridx[c] = read_index_generic(p.res_packed, p.res_bytes, v0 + c, p.res_bits);
+    }
+  }
+  if (p.groups_per_codebook > 0) {
+    const uint32_t off = (uint32_t)((kb * 8) / p.groups_per_codebook) * (uint32_t)p.num_centroids;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) idx[c] += off;
+  }
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    if (idx[c] >= (uint32_t)p.cb_rows || (has_res && ridx[c] >= (uint32_t)p.res_rows)) {
+      atomicExch(&g_gemm_status, 11);
+      idx[c] = 0;
+      ridx[c] = 0;
+    }
+  }
+  Half8 cv[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) cv[c] = ldg_vec(reinterpret_cast<const Half8*>(p.centroids) + idx[c]);
+  __half2 s2 = __float2half2_rn(1.f);
+  const bool has_scale = p.row_scale != nullptr;
+  if (has_scale) s2 = __half2half2(__ldg(p.row_scale + n));
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    __half2 h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = cv[c].h[i];
+    if (has_res) {
+      const Half8 r = ldg_vec(reinterpret_cast<const Half8*>(p.res_centroids) + ridx[c]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[i] = __hadd2_rn(h[i], r.h[i]);
+    }
+    if (has_scale) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) h[i] = __hmul2_rn(h[i], s2);
+    }
+    st_shared_v4(row_addr + ((c ^ sw) << 4), pack_half8<T>(h));
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void decode_q4_row(const FusedQ4& p, int n, int N, int K, int kb,
+                                              uint32_t b_stage, int row) {
+  const uint32_t row_addr = b_stage + row * 128;
+  const int sw = row & 7;
+  if (n >= N) {
+    const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) st_shared_v4(row_addr + ((c ^ sw) << 4), z);
+    return;
+  }
+  const int groups = K / p.group_size;
+  const uint8_t* cp = p.codes + (size_t)n * (K / 2) + kb * 32;
+  const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(cp));
+  const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(cp) + 1);
+  const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const int g = (kb * 64 + c * 8) / p.group_size;
+    const float s = __half2float(__ldg(p.scale + (size_t)n * groups + g));
+    const float z = p.zp ? __half2float(__ldg(p.zp + (size_t)n * groups + g)) : 8.f;
+    T v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      v[e] = from_f32<T>(__fmul_rn(__fsub_rn((float)((words[c] >> (4 * e)) & 0xfu), z), s));
+    st_shared_v4(row_addr + ((c ^ sw) << 4), *reinterpret_cast<const uint4*>(v));
+  }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+template <typename T, int BN, int MT, int BMODE, int BITS>
+__global__ void __launch_bounds__(BMODE == B_TMA ? 192 : 320, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmParams p, const int stages) {
+  constexpr int ACC_COLS = MT * BN;                       // fp32 columns per accumulator buffer
+  constexpr int NBUF = (2 * ACC_COLS <= 512) ? 2 : 1;
+  constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 32) ? 32 : (NBUF * ACC_COLS <= 64) ? 64
+                          : (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256) ? 256 : 512;
+  constexpr int BUF_STRIDE = (NBUF == 2) ? TMEM_COLS / 2 : 0;
+  constexpr int kStageBytes = SmemLayout<BN, MT>::kStageBytes;
+  constexpr int kNumDecodeWarps = (BMODE == B_TMA) ? 0 : 4;
+  constexpr uint32_t kIdesc = umma_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
+  static_assert(BMODE == B_TMA || BN == 128, "fused decode maps one decode thread to one W row");
+
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: swizzle atoms of TMA and UMMA are anchored at multiples of 1024.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);          // [stages]
+  uint64_t* empty_bar = full_bar + 8;                              // [stages]
+  uint64_t* tmem_full = empty_bar + 8;                             // [2]
+  uint64_t* tmem_empty = tmem_full + 2;                            // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* stage_base = smem + SmemLayout<BN, MT>::kBarrierBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1 + kNumDecodeWarps);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 4);  // one arrive per epilogue warp
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    if (BMODE == B_TMA) tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs)) {
+            atomicExch(&g_gemm_status, 1);
+            ok = false;
+            break;
+          }
+          uint8_t* st = stage_base + (size_t)s * kStageBytes;
+          constexpr uint32_t tx = MT * kAStageBytes + (BMODE == B_TMA ? BN * BK * 2 : 0);
+          mbar_arrive_expect_tx(&full_bar[s], tx);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            tma_load_2d(st + mt * kAStageBytes, &tmap_a, &full_bar[s], kb * BK,
+                        (tm * MT + mt) * BM);
+          if (BMODE == B_TMA)
+            tma_load_2d(st + MT * kAStageBytes, &tmap_b, &full_bar[s], kb * BK, tn * BN);
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = (NBUF == 2) ? (it & 1) : 0;
+        const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
+        if (!mbar_wait_bounded(&tmem_empty[buf], buf_ph ^ 1, abort_flag, kWaitTimeoutNs)) {
+          atomicExch(&g_gemm_status, 2);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + buf * BUF_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, kWaitTimeoutNs)) {
+            atomicExch(&g_gemm_status, 2);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t st = smem_u32(stage_base + (size_t)s * kStageBytes);
+          const uint64_t bdesc = umma_desc_sw128(st + MT * kAStageBytes);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint64_t adesc = umma_desc_sw128(st + mt * kAStageBytes);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // +32 bytes per K step inside the 128-byte swizzle row: +2 in the >>4 field
+              umma_f16(acc + mt * BN, adesc + 2 * k, bdesc + 2 * k, kIdesc,
+                       (kb > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[buf]);
+      }
+    }
+  } else if (warp < 6) {
+    // ================= epilogue: TMEM -> registers -> global =================
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
+    T* y = static_cast<T*>(p.y);
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const int buf = (NBUF == 2) ? (it & 1) : 0;
+      const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
+      // All lanes wait (each needs the acquire), then agree on the outcome so that the
+      // warp-collective tcgen05.ld below is never reached by part of a warp.
+      const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, kWaitTimeoutNs);
+      if (!__all_sync(0xffffffffu, got)) {
+        atomicExch(&g_gemm_status, 3);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t acc = tmem_base + buf * BUF_STRIDE + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+        const int m = (tm * MT + mt) * BM + quad * 32 + lane;
+        // Rows past M hold zeros (TMA zero fill); whole sub-tiles past M are skipped by all
+        // lanes together so the tcgen05.ld stays warp-uniform.
+        if ((tm * MT + mt) * BM >= p.M) break;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(acc + mt * BN + c * 32, v);
+          tmem_ld_wait();
+          const int n0 = tn * BN + c * 32;
+          if (m < p.M && n0 < p.N) {
+            T* dst = y + (size_t)m * p.N + n0;
+            const bool full = (n0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+            if (full) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                struct alignas(16) Out { T e[8]; } o;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  float f = __uint_as_float(v[q * 8 + e]);
+                  if (p.bias) f += __ldg(p.bias + n0 + q * 8 + e);
+                  o.e[e] = from_f32<T>(f);
+                }
+                reinterpret_cast<Out*>(dst)[q] = o;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                if (n0 + e < p.N) {
+                  float f = __uint_as_float(v[e]);
+                  if (p.bias) f += __ldg(p.bias + n0 + e);
+                  dst[e] = from_f32<T>(f);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+    }
+  } else {
+    // ================= B decoders (fused modes only) =================
+    if constexpr (BMODE != B_TMA) {
+      const int row = threadIdx.x - 6 * 32;  // 0..127
+      const int G = p.K / 8;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int tn = t / p.tiles_m;
+        const int n = tn * BN + row;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const bool got = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs);
+          if (!__all_sync(0xffffffffu, got)) {
+            atomicExch(&g_gemm_status, 4);
+            ok = false;
+            break;
+          }
+          const uint32_t b_stage = smem_u32(stage_base + (size_t)s * kStageBytes + MT * kAStageBytes);
+          if constexpr (BMODE == B_VQ) decode_vq_row<T, BITS>(p.vq, n, p.N, G, kb, b_stage, row);
+          else decode_q4_row<T>(p.q4, n, p.N, p.K, kb, b_stage, row);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[s]);
+          if (++s == stages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: everyone meets here, also after an abort ----
+  if (*abort_flag) {
+    // Let TMA copies that were already issued land before the shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major [rows, cols] matrix of 16-bit elements, box = [box_rows, 64 cols], 128B swizzle.
+int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int box_rows,
+              bool bf16) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) {
+    set_last_cuda_error(cudaErrorSymbolNotFound, "cuTensorMapEncodeTiled lookup");
+    return NPB_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                        2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+    return NPB_ERR_CUDA;
+  }
+  return NPB_OK;
+}
+
+template <typename T, int BN, int MT, int BMODE, int BITS>
+int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t st) {
+  constexpr bool bf16 = std::is_same<T, __nv_bfloat16>::value;
+  auto kern = gemm_kernel<T, BN, MT, BMODE, BITS>;
+  const int cap = max_dynamic_smem();
+  const int stages = SmemLayout<BN, MT>::stages(cap);
+  if (stages < 2) return NPB_ERR_UNSUPPORTED;
+  const int smem = SmemLayout<BN, MT>::kBarrierBytes + 1024 + stages * SmemLayout<BN, MT>::kStageBytes;
+  static int configured[64] = {0};
+  int dev = 0;
+  NPB_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && configured[dev] < smem) {
+    NPB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev] = smem;
+  }
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap(&ta, x, p.M, p.K, BM, bf16)) return rc;
+  if (BMODE == B_TMA) {
+    if (int rc = make_tmap(&tb, w_dense, p.N, p.K, BN, bf16)) return rc;
+  } else {
+    tb = ta;
+  }
+  p.tiles_m = (p.M + BM * MT - 1) / (BM * MT);
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  constexpr int threads = BMODE == B_TMA ? 192 : 320;
+  kern<<<grid, threads, smem, st>>>(ta, tb, p, stages);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+// Tile width for the dense GEMM: minimise (waves x tile cost) with a mild preference for
+// wide tiles (fewer shared-memory bytes per flop).
+int pick_bn(int64_t M, int64_t N) {
+  const int cands[5] = {256, 224, 192, 128, 64};
+  const int sms = sm_count();
+  const int64_t tm = (M + BM - 1) / BM;
+  double best = 1e30;
+  int best_bn = 256;
+  for (int bn : cands) {
+    const int64_t tiles = tm * ((N + bn - 1) / bn);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double eff = bn >= 192 ? 1.0 : bn == 128 ? 1.12 : 1.5;
+    const double cost = (double)waves * bn * eff;
+    if (cost < best - 1e-9) { best = cost; best_bn = bn; }
+  }
+  return best_bn;
+}
+
+template <typename T>
+int gemm_dense(const void* x, const void* w, GemmParams p, cudaStream_t st) {
+  switch (pick_bn(p.M, p.N)) {
+    case 256: return launch_gemm<T, 256, 1, B_TMA, 0>(x, w, p, st);
+    case 224: return launch_gemm<T, 224, 1, B_TMA, 0>(x, w, p, st);
+    case 192: return launch_gemm<T, 192, 1, B_TMA, 0>(x, w, p, st);
+    case 128: return launch_gemm<T, 128, 1, B_TMA, 0>(x, w, p, st);
+    default: return launch_gemm<T, 64, 1, B_TMA, 0>(x, w, p, st);
+  }
+}
+
+template <typename T, int BMODE, int BITS>
+int gemm_fused_mt(const void* x, GemmParams p, cudaStream_t st) {
+  const int mt = p.M <= 128 ? 1 : p.M <= 256 ? 2 : 3;
+  switch (mt) {
+    case 1: return launch_gemm<T, 128, 1, BMODE, BITS>(x, nullptr, p, st);
+    case 2: return launch_gemm<T, 128, 2, BMODE, BITS>(x, nullptr, p, st);
+    default: return launch_gemm<T, 128, 3, BMODE, BITS>(x, nullptr, p, st);
+  }
+}
+
+void fill_fused_vq(FusedVq& v, const npb_vq_weight* w, int64_t K) {
+  v.packed = w->packed;
+  v.packed_bytes = w->packed_bytes;
+  v.centroids = static_cast<const __half*>(w->centroids);
+  v.res_packed = w->res_packed;
+  v.res_bytes = w->res_packed_bytes;
+  v.res_centroids = static_cast<const __half*>(w->res_centroids);
+  v.row_scale = static_cast<const __half*>(w->row_scale);
+  v.bits = w->bits;
+  v.res_bits = w->res_bits;
+  v.num_centroids = w->num_centroids;
+  v.groups_per_codebook = w->cols_per_codebook > 0 ? w->cols_per_codebook / 8 : 0;
+  v.cb_rows = w->num_centroids *
+              (w->cols_per_codebook > 0 ? (int)((K + w->cols_per_codebook - 1) / w->cols_per_codebook) : 1);
+  v.res_rows = w->res_num_centroids;
+}
+
+// Which index-read specialisation the tile decoder can use for this weight (0 = generic).
+int fused_vq_bits(const npb_vq_weight* w, const FusedVq& v) {
+  if ((w->bits == 16 || w->bits == 12 || w->bits == 8) &&
+      aligned_to(w->packed, index8_alignment(w->bits)) && (v.groups_per_codebook % 8 == 0) &&
+      (!w->res_packed || (w->res_bits == 8 && aligned_to(w->res_packed, 8))))
+    return w->bits;
+  return 0;
+}
+
+// Test hook: decode one 128-row x 64-column W tile exactly as the fused GEMM's decoder warps
+// do (same function, same swizzled layout) and copy the 16 KiB tile image to global memory.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(128) vq_tile_probe_kernel(FusedVq v, int N, int K, int tn, int kb,
+                                                            uint4* __restrict__ out) {
+  __shared__ __align__(1024) uint8_t tile[128 * 128];
+  const int row = threadIdx.x;
+  decode_vq_row<T, BITS>(v, tn * 128 + row, N, K / 8, kb, smem_u32(tile), row);
+  __syncthreads();
+  for (int i = threadIdx.x; i < 128 * 8; i += 128) out[i] = reinterpret_cast<const uint4*>(tile)[i];
+}
+
+template <typename T>
+int launch_tile_probe(const FusedVq& v, int vbits, int N, int K, int tn, int kb, void* out,
+                      cudaStream_t st) {
+  uint4* o = static_cast<uint4*>(out);
+  switch (vbits) {
+    case 16: vq_tile_probe_kernel<T, 16><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
+    case 12: vq_tile_probe_kernel<T, 12><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
+    case 8: vq_tile_probe_kernel<T, 8><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
+    default: vq_tile_probe_kernel<T, 0><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
+  }
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+int check_gemm_common(const void* x, const void* y, int64_t M, int64_t N, int64_t K, int dtype) {
+  if (M < 0 || N < 0 || K < 0) return NPB_ERR_INVALID_ARG;
+  if (dtype != NPB_BF16 && dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
+  if (M == 0 || N == 0) return NPB_OK;
+  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (K == 0 || K % 8 != 0) return NPB_ERR_SHAPE;
+  if (!aligned_to(x, 16)) return NPB_ERR_ALIGNMENT;
+  if (M >= (int64_t)1 << 31 || N >= (int64_t)1 << 31 || K >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
+  return NPB_OK;
+}
+
+}  // namespace
+
+int gemm(const void* x, const void* w, const float* bias, void* y, int64_t M, int64_t N, int64_t K,
+         int dtype, cudaStream_t st) {
+  if (int rc = check_gemm_common(x, y, M, N, K, dtype)) return rc;
+  if (M == 0 || N == 0) return NPB_OK;
+  if (w == nullptr) return NPB_ERR_INVALID_ARG;
+  if (!aligned_to(w, 16)) return NPB_ERR_ALIGNMENT;
+  GemmParams p{};
+  p.bias = bias;
+  p.y = y;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  return dtype == NPB_BF16 ? gemm_dense<__nv_bfloat16>(x, w, p, st) : gemm_dense<__half>(x, w, p, st);
+}
+
+int vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
+                  int64_t K, const float* bias, void* y, cudaStream_t st) {
+  if (int rc = validate_vq(w, N, K)) return rc;
+  if (int rc = check_gemm_common(x, y, M, N, K, x_dtype)) return rc;
+  if (M == 0 || N == 0) return NPB_OK;
+  if (w->vector_len != 8 || K % 64 != 0) return NPB_ERR_UNSUPPORTED;
+  if (!aligned_to(w->centroids, 16) || (w->res_centroids && !aligned_to(w->res_centroids, 16)))
+    return NPB_ERR_ALIGNMENT;
+  GemmParams p{};
+  p.bias = bias;
+  p.y = y;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  fill_fused_vq(p.vq, w, K);
+  const int vbits = fused_vq_bits(w, p.vq);
+  if (vbits == 0 && p.vq.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
+  const bool bf = x_dtype == NPB_BF16;
+  switch (vbits) {
+    case 16: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 16>(x, p, st) : gemm_fused_mt<__half, B_VQ, 16>(x, p, st);
+    case 12: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 12>(x, p, st) : gemm_fused_mt<__half, B_VQ, 12>(x, p, st);
+    case 8: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 8>(x, p, st) : gemm_fused_mt<__half, B_VQ, 8>(x, p, st);
+    default: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 0>(x, p, st) : gemm_fused_mt<__half, B_VQ, 0>(x, p, st);
+  }
+}
+
+int vq_decode_tile_probe(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
+                         int dtype, void* out, cudaStream_t st) {
+  if (int rc = validate_vq(w, N, K)) return rc;
+  if (out == nullptr || w->vector_len != 8 || K % 64 != 0 || N <= 0) return NPB_ERR_UNSUPPORTED;
+  if (dtype != NPB_BF16 && dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
+  if (tile_n < 0 || (int64_t)tile_n * 128 >= N || k_block < 0 || (int64_t)k_block * 64 >= K)
+    return NPB_ERR_INVALID_ARG;
+  if (!aligned_to(out, 16) || !aligned_to(w->centroids, 16) ||
+      (w->res_centroids && !aligned_to(w->res_centroids, 16)))
+    return NPB_ERR_ALIGNMENT;
+  FusedVq v{};
+  fill_fused_vq(v, w, K);
+  const int vbits = fused_vq_bits(w, v);
+  if (vbits == 0 && v.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
+  return dtype == NPB_BF16
+             ? launch_tile_probe<__nv_bfloat16>(v, vbits, (int)N, (int)K, tile_n, k_block, out, st)
+             : launch_tile_probe<__half>(v, vbits, (int)N, (int)K, tile_n, k_block, out, st);
+}
+
+int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                 const float* bias, void* y, cudaStream_t st) {
+  if (int rc = validate_q(w, N, K)) return rc;
+  if (int rc = check_gemm_common(x, y, M, N, K, x_dtype)) return rc;
+  if (M == 0 || N == 0) return NPB_OK;
+  if (w->nbits != 4 || K % 64 != 0) return NPB_ERR_UNSUPPORTED;
+  if (!aligned_to(w->codes, 16)) return NPB_ERR_ALIGNMENT;
+  GemmParams p{};
+  p.bias = bias;
+  p.y = y;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.q4.codes = w->codes;
+  p.q4.scale = static_cast<const __half*>(w->scale);
+  p.q4.zp = static_cast<const __half*>(w->zero_point);
+  p.q4.group_size = w->group_size;
+  return x_dtype == NPB_BF16 ? gemm_fused_mt<__nv_bfloat16, B_Q4, 0>(x, p, st)
+                             : gemm_fused_mt<__half, B_Q4, 0>(x, p, st);
+}
+
+// Reads and clears the device-side give-up record of the GEMM kernels (synchronises).
+int gemm_device_status(int* host_out) {
+  int v = 0;
+  NPB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)));
+  if (v != 0) {
+    const int zero = 0;
+    NPB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+  }
+  if (host_out) *host_out = v;
+  return v == 0 ? NPB_OK : NPB_ERR_DEVICE_TIMEOUT;
+}
+
+}  // namespace npb

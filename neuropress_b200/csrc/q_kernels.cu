@@ -1,0 +1,330 @@
+// Group-affine (Q4_0 / HQQ style) weights: one-pass decode and fused GEMV.
+//
+//   W[n, k] = convert_T( (float(q[n,k]) - zp[n, k/g]) * float(s[n, k/g]) )
+//
+// q is nbits wide, packed LSB-first inside each byte of codes[N, K*nbits/8]; zp is the fp16
+// zero-point or the constant 2^(nbits-1).  The arithmetic (fp32 subtract, fp32 multiply, one
+// rounding to T) is that of _q_dequant_linear (neuropress/nn/np_linear.py:334-351) and of the
+// reference kernel (neuropress/kernels/q4_linear.cu:101-123); __fmul_rn / __fsub_rn keep the
+// compiler from contracting them, so the decode is bit-exact.
+//
+// GEMV: a warp owns one output row; each lane loads 16 bytes of codes (32 nibbles) per step,
+// so a warp reads 512 contiguous bytes.  Per lane and step the dot product uses
+//   sum_k x_k (q_k - zp) s  =  s * (sum_k x_k q_k  -  zp * sum_k x_k)
+// with sum_k x_k over each 8-element chunk precomputed once per CTA.  fp32 accumulation.
+// HBM bytes per call: N*K*nbits/8 + 2*(1 or 2)*N*K/g + activations — pure streaming.
+#include "common.cuh"
+
+namespace npb {
+namespace {
+
+// ------------------------------------------------------------------ decode ------------
+constexpr int kDecThreads = 256;
+
+template <typename T, int NBITS>
+__global__ void __launch_bounds__(kDecThreads)
+q_decode_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ scale,
+                const __half* __restrict__ zp, T* __restrict__ out, int64_t n_chunks,
+                int group_size) {
+  // One thread decodes 8 consecutive values (one 8-element chunk never straddles a group:
+  // group_size % 8 == 0).
+  constexpr int BYTES = NBITS;  // 8 values * NBITS / 8
+  const int64_t c = (int64_t)blockIdx.x * kDecThreads + threadIdx.x;
+  if (c >= n_chunks) return;
+  const int64_t e0 = c * 8;
+  const int64_t gi = e0 / group_size;
+  const float s = __half2float(__ldg(scale + gi));
+  const float z = zp ? __half2float(__ldg(zp + gi)) : (float)(1 << (NBITS - 1));
+  uint32_t q[8];
+  if constexpr (NBITS == 4) {
+    const uint32_t r = __ldg(reinterpret_cast<const uint32_t*>(codes + c * BYTES));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = (r >> (4 * i)) & 0xfu;
+  } else {
+    const uint2 r = __ldg(reinterpret_cast<const uint2*>(codes + c * BYTES));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { q[i] = (r.x >> (8 * i)) & 0xffu; q[4 + i] = (r.y >> (8 * i)) & 0xffu; }
+  }
+  float w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) w[i] = __fmul_rn(__fsub_rn((float)q[i], z), s);
+  if constexpr (sizeof(T) == 2) {
+    struct alignas(16) Out { T v[8]; } o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = from_f32<T>(w[i]);
+    *reinterpret_cast<Out*>(out + e0) = o;
+  } else {
+    reinterpret_cast<float4*>(out + e0)[0] = make_float4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<float4*>(out + e0)[1] = make_float4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+template <typename T>
+int launch_decode(const npb_q_weight* w, int64_t N, int64_t K, T* out, cudaStream_t st) {
+  const int64_t n_chunks = N * K / 8;
+  const int64_t blocks = (n_chunks + kDecThreads - 1) / kDecThreads;
+  if (blocks >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
+  const __half* s = static_cast<const __half*>(w->scale);
+  const __half* z = static_cast<const __half*>(w->zero_point);
+  if (w->nbits == 4)
+    q_decode_kernel<T, 4><<<(unsigned)blocks, kDecThreads, 0, st>>>(w->codes, s, z, out, n_chunks, w->group_size);
+  else
+    q_decode_kernel<T, 8><<<(unsigned)blocks, kDecThreads, 0, st>>>(w->codes, s, z, out, n_chunks, w->group_size);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+// ------------------------------------------------------------------ GEMV --------------
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+
+struct QGemvArgs {
+  const uint8_t* codes;
+  const __half* scale;
+  const __half* zp;
+  const float* bias;
+  const void* x;
+  void* y;
+  int M, N, K, group_size;
+};
+
+// Shared memory: x as fp32?  No: x stays in T, [MT][K] with the same XOR swizzle on 8-element
+// chunks as the VQ GEMV (a lane's 32 values are 4 consecutive chunks), plus fp32 chunk sums
+// xsum[MT][K/8].
+__device__ __forceinline__ int swz8(int j) { return (j ^ ((j >> 3) & 7)) * 8; }
+
+template <typename T>
+__device__ __forceinline__ void load8f(const T* p, float (&f)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
+  } else {
+    const float4 a = reinterpret_cast<const float4*>(p)[0];
+    const float4 b = reinterpret_cast<const float4*>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+}
+
+template <typename T, int MT, int ROWS>
+__global__ void __launch_bounds__(kThreads) q4_gemv_kernel(QGemvArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int K = a.K;
+  const int chunks = K / 8;
+  T* xs = reinterpret_cast<T*>(smem);                                   // [MT][K]
+  float* xsum = reinterpret_cast<float*>(smem + (size_t)MT * K * sizeof(T));  // [MT][chunks]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  {
+    const T* x = static_cast<const T*>(a.x);
+    for (int t = tid; t < MT * chunks; t += kThreads) {
+      const int m = t / chunks, j = t - m * chunks;
+      T* dst = xs + (size_t)m * K + swz8(j);
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const T v = (m < a.M) ? x[(size_t)m * K + j * 8 + e] : from_f32<T>(0.f);
+        dst[e] = v;
+        s += to_f32(v);
+      }
+      xsum[m * chunks + j] = s;
+    }
+  }
+  __syncthreads();
+
+  const int gs = a.group_size;
+  const int groups = K / gs;
+  const int row_bytes = K / 2;
+  const int warps_total = gridDim.x * kWarps;
+  for (int n0 = (blockIdx.x * kWarps + warp) * ROWS; n0 < a.N; n0 += warps_total * ROWS) {
+    float acc[ROWS][MT];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+
+    for (int k0 = lane * 32; k0 < K; k0 += 1024) {
+      uint4 code[ROWS];
+      float sc[ROWS], zo[ROWS];
+      const int g = k0 / gs;  // the lane's 32 values lie inside one group (gs % 32 == 0)
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int n = n0 + r < a.N ? n0 + r : a.N - 1;
+        code[r] = __ldg(reinterpret_cast<const uint4*>(a.codes + (size_t)n * row_bytes + k0 / 2));
+        sc[r] = __half2float(__ldg(a.scale + (size_t)n * groups + g));
+        zo[r] = 128.f + (a.zp ? __half2float(__ldg(a.zp + (size_t)n * groups + g)) : 8.f);
+      }
+      float d[ROWS][MT];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) d[r][m] = 0.f;
+      const int j0 = k0 / 8;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        const int pos = swz8(j0 + ch);
+        float xv[MT][8];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) load8f<T>(xs + (size_t)m * K + pos, xv[m]);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          const uint32_t word = ch == 0 ? code[r].x : ch == 1 ? code[r].y : ch == 2 ? code[r].z : code[r].w;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            // fp32 bit pattern of 128 + q: the nibble dropped into the top mantissa bits of
+            // 128.0f (ulp 2^-16 ... bit 16 has weight 1).
+            const uint32_t sh = e <= 4 ? (word << (16 - 4 * e)) : (word >> (4 * e - 16));
+            const float qf = __uint_as_float(0x43000000u | (sh & 0x000f0000u));
+#pragma unroll
+            for (int m = 0; m < MT; ++m) d[r][m] = fmaf(qf, xv[m][e], d[r][m]);
+          }
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float4 s4 = *reinterpret_cast<const float4*>(xsum + m * chunks + j0);
+        const float xs32 = (s4.x + s4.y) + (s4.z + s4.w);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+          acc[r][m] = fmaf(sc[r], d[r][m] - zo[r] * xs32, acc[r][m]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane == 0) {
+      T* y = static_cast<T*>(a.y);
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int n = n0 + r;
+        if (n >= a.N) continue;
+        const float b = a.bias ? __ldg(a.bias + n) : 0.f;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+          if (m < a.M) y[(size_t)m * a.N + n] = from_f32<T>(acc[r][m] + b);
+      }
+    }
+  }
+}
+
+// Fallback for shapes the streaming kernel does not take (K % 32 != 0, 8-bit codes):
+// a warp per row, one 8-value chunk per lane and step.
+template <typename T, int NBITS>
+__global__ void __launch_bounds__(kThreads) q_gemv_generic_kernel(QGemvArgs a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int K = a.K, gs = a.group_size, groups = K / gs;
+  const int row_bytes = K * NBITS / 8;
+  const T* x = static_cast<const T*>(a.x);
+  T* y = static_cast<T*>(a.y);
+  for (int n = blockIdx.x * kWarps + warp; n < a.N; n += gridDim.x * kWarps) {
+    for (int m = 0; m < a.M; ++m) {
+      float acc = 0.f;
+      for (int j = lane; j < K / 8; j += 32) {
+        const int g = (j * 8) / gs;
+        const float s = __half2float(__ldg(a.scale + (size_t)n * groups + g));
+        const float z = a.zp ? __half2float(__ldg(a.zp + (size_t)n * groups + g))
+                             : (float)(1 << (NBITS - 1));
+        const uint8_t* cp = a.codes + (size_t)n * row_bytes + (size_t)j * NBITS;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          uint32_t q;
+          if constexpr (NBITS == 4) q = (__ldg(cp + e / 2) >> (4 * (e & 1))) & 0xfu;
+          else q = __ldg(cp + e);
+          acc = fmaf(((float)q - z) * s, to_f32(x[(size_t)m * K + j * 8 + e]), acc);
+        }
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) y[(size_t)m * a.N + n] = from_f32<T>(acc + (a.bias ? a.bias[n] : 0.f));
+    }
+  }
+}
+
+template <typename KernT>
+int launch_persistent(KernT kern, const QGemvArgs& a, size_t smem, int rows_per_warp,
+                      cudaStream_t st) {
+  if (smem > 48 * 1024)
+    NPB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  NPB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
+  if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
+  const int rows_per_block = kWarps * rows_per_warp;
+  const int want = (a.N + rows_per_block - 1) / rows_per_block;
+  const int cap = sm_count() * per_sm;
+  kern<<<want < cap ? want : cap, kThreads, smem, st>>>(a);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+template <typename T>
+int run_gemv(const npb_q_weight* w, QGemvArgs a, cudaStream_t st) {
+  const bool fast = w->nbits == 4 && a.K % 1024 == 0 && w->group_size % 32 == 0 &&
+                    aligned_to(a.codes, 16);
+  if (!fast) {
+    if (w->nbits == 4) return launch_persistent(q_gemv_generic_kernel<T, 4>, a, 0, 1, st);
+    return launch_persistent(q_gemv_generic_kernel<T, 8>, a, 0, 1, st);
+  }
+  const int M = a.M;
+  int batch = 8;
+  auto need = [&](int mt) { return (size_t)mt * a.K * sizeof(T) + (size_t)mt * (a.K / 8) * 4; };
+  while (batch > 1 && need(batch) > (size_t)max_dynamic_smem() / 2) batch >>= 1;
+  if (need(batch) > (size_t)max_dynamic_smem()) return NPB_ERR_TOO_LARGE;
+  for (int m0 = 0; m0 < M; m0 += batch) {
+    QGemvArgs b = a;
+    b.M = (M - m0) < batch ? (M - m0) : batch;
+    b.x = static_cast<const T*>(a.x) + (size_t)m0 * a.K;
+    b.y = static_cast<T*>(a.y) + (size_t)m0 * a.N;
+    const int mt = b.M <= 1 ? 1 : b.M <= 2 ? 2 : b.M <= 4 ? 4 : 8;
+    int rc;
+    switch (mt) {
+      case 1: rc = launch_persistent(q4_gemv_kernel<T, 1, 2>, b, need(1), 2, st); break;
+      case 2: rc = launch_persistent(q4_gemv_kernel<T, 2, 2>, b, need(2), 2, st); break;
+      case 4: rc = launch_persistent(q4_gemv_kernel<T, 4, 1>, b, need(4), 1, st); break;
+      default: rc = launch_persistent(q4_gemv_kernel<T, 8, 1>, b, need(8), 1, st); break;
+    }
+    if (rc) return rc;
+  }
+  return NPB_OK;
+}
+
+}  // namespace
+
+int q_decode(const npb_q_weight* w, int64_t N, int64_t K, void* out, int out_dtype,
+             cudaStream_t st) {
+  if (int rc = validate_q(w, N, K)) return rc;
+  if (N * K == 0) return NPB_OK;
+  if (out == nullptr) return NPB_ERR_INVALID_ARG;
+  if (!aligned_to(out, 16) || !aligned_to(w->codes, w->nbits == 4 ? 4 : 8)) return NPB_ERR_ALIGNMENT;
+  switch (out_dtype) {
+    case NPB_BF16: return launch_decode<__nv_bfloat16>(w, N, K, static_cast<__nv_bfloat16*>(out), st);
+    case NPB_F16: return launch_decode<__half>(w, N, K, static_cast<__half*>(out), st);
+    case NPB_F32: return launch_decode<float>(w, N, K, static_cast<float*>(out), st);
+    default: return NPB_ERR_UNSUPPORTED;
+  }
+}
+
+int q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+           const float* bias, void* y, cudaStream_t st) {
+  if (int rc = validate_q(w, N, K)) return rc;
+  if (M < 0 || M > NPB_GEMV_MAX_ROWS) return NPB_ERR_UNSUPPORTED;
+  if (M == 0 || N == 0) return NPB_OK;
+  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (N >= (int64_t)1 << 31 || K >= (int64_t)1 << 24) return NPB_ERR_UNSUPPORTED;
+  QGemvArgs a{};
+  a.codes = w->codes;
+  a.scale = static_cast<const __half*>(w->scale);
+  a.zp = static_cast<const __half*>(w->zero_point);
+  a.bias = bias;
+  a.x = x;
+  a.y = y;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.group_size = w->group_size;
+  switch (x_dtype) {
+    case NPB_BF16: return run_gemv<__nv_bfloat16>(w, a, st);
+    case NPB_F16: return run_gemv<__half>(w, a, st);
+    case NPB_F32: return run_gemv<float>(w, a, st);
+    default: return NPB_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace npb

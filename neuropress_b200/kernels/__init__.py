@@ -1,0 +1,306 @@
+"""Python wrappers over the C ABI, named after the reference's ``neuropress.kernels`` functions.
+
+Reference (neuropress/kernels/__init__.py): ``vq_dequant`` :497-529, ``vq_linear`` (GEMV for
+any row count), ``vq_linear_wmma`` :335-352, ``q_linear`` :109-151, ``warn_kernel_fallback``
+:436-453; ``vq_gemm_triton`` (neuropress/kernels/vq_triton.py:119-179).  Each wrapper allocates
+its output with torch (the C ABI never allocates), validates like the reference's
+``TORCH_CHECK``s and raises ``RuntimeError`` on any failure.  Nothing here falls back to
+PyTorch math.
+
+The optional keyword arguments ``residual_indices``, ``residual_centroids``, ``residual_bits``,
+``row_scale`` and ``cols_per_codebook`` select the extended weight forms (residual codebook,
+per-output-row fp16 scale, one codebook per block of input columns); they default to the
+reference's plain form.
+"""
+
+from __future__ import annotations
+
+import logging
+
+import torch
+
+from .. import _cabi
+
+log = logging.getLogger(__name__)
+
+GEMV_MAX_ROWS = _cabi.GEMV_MAX_ROWS
+
+# ---------------------------------------------------------------------------
+# Fallback reporting (kept for build-failure reporting only: there is no fallback path)
+# ---------------------------------------------------------------------------
+
+_warned_fallbacks: set[str] = set()
+
+
+def warn_kernel_fallback(kernel: str, fallback: str, exc: BaseException) -> None:
+    """Warn once per *kernel* that it is unavailable (reference: kernels/__init__.py:436-453)."""
+    if kernel in _warned_fallbacks:
+        return
+    _warned_fallbacks.add(kernel)
+    log.warning(
+        "CUDA kernel %s unavailable (%s); %s. Build the library with "
+        "`python -m neuropress_b200.build` (nvcc with sm_100a support).",
+        kernel, exc, fallback,
+    )
+
+
+def _bias_f32(bias: torch.Tensor | None, n: int, device: torch.device) -> torch.Tensor | None:
+    """The reference re-casts the bias to fp32 on every call (vq_linear_wmma.cu:512-515)."""
+    if bias is None:
+        return None
+    if bias.numel() != n:
+        raise RuntimeError(f"bias must have {n} elements, got {bias.numel()}.")
+    b = bias.detach()
+    if b.dtype != torch.float32 or b.device != device or not b.is_contiguous():
+        b = b.to(device=device, dtype=torch.float32).contiguous()
+    return b
+
+
+def _vq_ext(ext: dict) -> dict:
+    allowed = {"residual_indices", "residual_centroids", "residual_bits", "row_scale",
+               "cols_per_codebook"}
+    unknown = set(ext) - allowed
+    if unknown:
+        raise TypeError(f"unknown keyword argument(s): {sorted(unknown)}")
+    return {k: v for k, v in ext.items() if v is not None}
+
+
+def _infer_n(packed: torch.Tensor, bits: int, k: int, vl: int) -> int:
+    """Output rows from the stream length, as vq_linear_wmma.cu:501-506 does."""
+    if k % vl:
+        raise RuntimeError(f"in_features={k} is not a multiple of vector_len={vl}.")
+    g = k // vl
+    n = (packed.numel() * 8) // (bits * g)
+    if n <= 0:
+        raise RuntimeError("packed buffer too short for one output row.")
+    return n
+
+
+# ---------------------------------------------------------------------------
+# VQ
+# ---------------------------------------------------------------------------
+
+
+def vq_dequant(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
+               out_features: int, in_features: int, dtype: torch.dtype, *,
+               out: torch.Tensor | None = None, **ext) -> torch.Tensor:
+    """Decode a packed VQ weight to a dense ``[out_features, in_features]`` tensor of *dtype*
+    in one kernel pass (reference: kernels/__init__.py:497-529, vq_dequant.cu:105-146)."""
+    ext = _vq_ext(ext)
+    _cabi.require_cuda("vq_dequant", packed_indices, centroids, ext.get("residual_indices"),
+                       ext.get("residual_centroids"), ext.get("row_scale"))
+    lib = _cabi.load_library()
+    w = _cabi.vq_struct(packed_indices, centroids, bits, **ext)
+    if out is None:
+        out = torch.empty((out_features, in_features), dtype=dtype, device=packed_indices.device)
+    elif out.shape != (out_features, in_features) or out.dtype != dtype or not out.is_contiguous():
+        raise RuntimeError("vq_dequant: `out` has the wrong shape, dtype or layout.")
+    with torch.cuda.device(packed_indices.device):
+        rc = lib.npb_vq_decode(w, out_features, in_features, out.data_ptr(),
+                               _cabi.dtype_code(dtype), _cabi.stream_ptr())
+    _cabi.check(rc, "vq_dequant")
+    return out
+
+
+def _vq_call(fn_name: str, x: torch.Tensor, packed: torch.Tensor, centroids: torch.Tensor,
+             bits: int, out_features: int | None, bias: torch.Tensor | None, ext: dict) -> torch.Tensor:
+    ext = _vq_ext(ext)
+    if x.dim() != 2:
+        raise RuntimeError(f"{fn_name}: x must be 2-D [M, K].")
+    _cabi.require_cuda(fn_name, x, packed, centroids, ext.get("residual_indices"),
+                       ext.get("residual_centroids"), ext.get("row_scale"))
+    lib = _cabi.load_library()
+    m, k = x.shape
+    vl = centroids.shape[-1]
+    n = out_features if out_features is not None else _infer_n(packed, bits, k, vl)
+    w = _cabi.vq_struct(packed, centroids, bits, **ext)
+    b = _bias_f32(bias, n, x.device)
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = getattr(lib, fn_name)(w, x.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
+                                   None if b is None else b.data_ptr(), y.data_ptr(),
+                                   _cabi.stream_ptr())
+    _cabi.check(rc, fn_name)
+    return y
+
+
+def vq_gemv(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
+            out_features: int | None = None, bias: torch.Tensor | None = None, **ext) -> torch.Tensor:
+    """Fused index-decode GEMV, ``x`` is ``[M, K]`` with ``M <= GEMV_MAX_ROWS``; fp16, bf16 or
+    fp32 activations; output in ``x.dtype``."""
+    return _vq_call("npb_vq_gemv", x, packed_indices, centroids, bits, out_features, bias, ext)
+
+
+def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
+                  bits: int, out_features: int | None = None, bias: torch.Tensor | None = None,
+                  **ext) -> torch.Tensor:
+    """Tile-decode tensor-core GEMM (tcgen05): same signature as the reference's
+    ``vq_gemm_triton`` (vq_triton.py:119-179).  bf16 / fp16 activations, vector length 8,
+    ``K % 64 == 0``."""
+    return _vq_call("npb_vq_gemm_fused", x, packed_indices, centroids, bits, out_features, bias, ext)
+
+
+def vq_linear(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
+              vector_len: int, bias: torch.Tensor | None = None, **ext) -> torch.Tensor:
+    """Fused VQ linear for any row count (reference: ``vq_linear``, vq_linear.cu:344-424).
+    Up to ``GEMV_MAX_ROWS`` rows run the GEMV; more rows run the tile-decode GEMM."""
+    if centroids.shape[-1] != vector_len:
+        raise RuntimeError("vector_len does not match the codebook.")
+    if x.shape[0] <= GEMV_MAX_ROWS:
+        return vq_gemv(x, packed_indices, centroids, bits, None, bias, **ext)
+    return vq_gemm_fused(x, packed_indices, centroids, bits, None, bias, **ext)
+
+
+def vq_linear_wmma(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
+                   bits: int, vector_len: int = 4, bias: torch.Tensor | None = None,
+                   **ext) -> torch.Tensor:
+    """Drop-in for the reference's ``vq_linear_wmma`` (kernels/__init__.py:335-352): GEMV up to
+    8 rows, tensor-core GEMM above (vq_linear_wmma.cu:47,444).  Unlike the reference the
+    vector length is honoured (the reference kernel is compiled for 4 only)."""
+    return vq_linear(x, packed_indices, centroids, bits, centroids.shape[-1], bias, **ext)
+
+
+# ---------------------------------------------------------------------------
+# Dense tensor-core GEMM
+# ---------------------------------------------------------------------------
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x[M,K] @ w[N,K].T (+ bias)`` on the tcgen05 tensor cores, bf16 / fp16, fp32
+    accumulate.  Stands in for ``F.linear`` after the decode (np_vq_linear.py:1148)."""
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise RuntimeError("gemm: expected x [M, K] and w [N, K].")
+    if x.dtype != w.dtype:
+        raise RuntimeError("gemm: x and w must have the same dtype.")
+    _cabi.require_cuda("gemm", x, w)
+    lib = _cabi.load_library()
+    m, k = x.shape
+    n = w.shape[0]
+    b = _bias_f32(bias, n, x.device)
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.npb_gemm(x.data_ptr(), w.data_ptr(), None if b is None else b.data_ptr(),
+                          y.data_ptr(), m, n, k, _cabi.dtype_code(x.dtype), _cabi.stream_ptr())
+    _cabi.check(rc, "gemm")
+    return y
+
+
+# ---------------------------------------------------------------------------
+# Group-affine (Q4_0 / HQQ)
+# ---------------------------------------------------------------------------
+
+
+def _q_prepare(name, w_pack, scale, zero_point, nbits, group_size):
+    if w_pack.dim() != 2:
+        raise RuntimeError(f"{name}: w_pack must be 2-D [N, K*nbits/8].")
+    if nbits not in (4, 8):
+        raise RuntimeError(f"{name}: nbits must be 4 or 8, got {nbits}.")
+    n = w_pack.shape[0]
+    k = w_pack.shape[1] * (8 // nbits)
+    if group_size <= 0 or k % group_size:
+        raise RuntimeError(f"{name}: group_size must divide K={k}.")
+    n_groups = n * (k // group_size)
+    if scale.numel() != n_groups or (zero_point is not None and zero_point.numel() != n_groups):
+        raise RuntimeError(f"{name}: scale / zero_point must have N*K/group_size = {n_groups} elements.")
+    return n, k
+
+
+def q_dequant(w_pack: torch.Tensor, scale: torch.Tensor, nbits: int, group_size: int,
+              zero_point: torch.Tensor | None, dtype: torch.dtype) -> torch.Tensor:
+    """Dense ``[N, K]`` weight ``((q - zp) * s).to(dtype)`` (np_linear.py:334-351)."""
+    _cabi.require_cuda("q_dequant", w_pack, scale, zero_point)
+    n, k = _q_prepare("q_dequant", w_pack, scale, zero_point, nbits, group_size)
+    lib = _cabi.load_library()
+    w = _cabi.q_struct(w_pack, scale, zero_point, nbits, group_size)
+    out = torch.empty((n, k), dtype=dtype, device=w_pack.device)
+    with torch.cuda.device(w_pack.device):
+        rc = lib.npb_q_decode(w, n, k, out.data_ptr(), _cabi.dtype_code(dtype), _cabi.stream_ptr())
+    _cabi.check(rc, "q_dequant")
+    return out
+
+
+def _q_call(fn_name, x, w_pack, scale, nbits, group_size, zero_point, bias):
+    _cabi.require_cuda(fn_name, x, w_pack, scale, zero_point)
+    n, k = _q_prepare(fn_name, w_pack, scale, zero_point, nbits, group_size)
+    if x.shape[-1] != k:
+        raise RuntimeError(f"{fn_name}: x has {x.shape[-1]} columns, the weight has K={k}.")
+    lib = _cabi.load_library()
+    *leading, _ = x.shape
+    x2 = x.reshape(-1, k)
+    m = x2.shape[0]
+    w = _cabi.q_struct(w_pack, scale, zero_point, nbits, group_size)
+    b = _bias_f32(bias, n, x.device)
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = getattr(lib, fn_name)(w, x2.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
+                                   None if b is None else b.data_ptr(), y.data_ptr(),
+                                   _cabi.stream_ptr())
+    _cabi.check(rc, fn_name)
+    return y.reshape(*leading, n)
+
+
+def q_gemv(x, w_pack, scale, nbits, group_size, zero_point=None, bias=None) -> torch.Tensor:
+    """Fused unpack + dequant + dot for up to ``GEMV_MAX_ROWS`` rows."""
+    return _q_call("npb_q_gemv", x, w_pack, scale, nbits, group_size, zero_point, bias)
+
+
+def q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point=None, bias=None) -> torch.Tensor:
+    """Tile-dequant tensor-core GEMM for 4-bit codes (bf16 / fp16 activations)."""
+    return _q_call("npb_q_gemm_fused", x, w_pack, scale, nbits, group_size, zero_point, bias)
+
+
+# Row count up to which q_linear re-decodes the weight inside the GEMM; above it the weight is
+# decoded once and the dense GEMM runs (the tile-dequant GEMM repeats the decode per 384 rows).
+Q_FUSED_MAX_ROWS = 384
+
+
+def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: int,
+             group_size: int, zero_point: torch.Tensor | None = None,
+             bias: torch.Tensor | None = None) -> torch.Tensor:
+    """Drop-in for the reference's ``q_linear`` (kernels/__init__.py:109-151): ``x`` is
+    ``[..., K]``, output ``[..., N]`` in ``x.dtype``.  The reference runs one GEMV kernel for
+    every row count (q4_linear.cu:137-140); here rows are banded: GEMV, tile-dequant GEMM,
+    then decode once + dense GEMM."""
+    k = w_pack.shape[1] * (8 // nbits)
+    m = x.numel() // max(k, 1)
+    if m <= GEMV_MAX_ROWS:
+        return q_gemv(x, w_pack, scale, nbits, group_size, zero_point, bias)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("q_linear: more than 8 rows need fp16 or bf16 activations.")
+    if m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0:
+        return q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point, bias)
+    w = q_dequant(w_pack, scale, nbits, group_size, zero_point, x.dtype)
+    *leading, _ = x.shape
+    return gemm(x.reshape(-1, k), w, bias).reshape(*leading, w.shape[0])
+
+
+# ---------------------------------------------------------------------------
+# Test hook
+# ---------------------------------------------------------------------------
+
+
+def vq_decode_tile(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
+                   out_features: int, in_features: int, tile_n: int, k_block: int,
+                   dtype: torch.dtype, **ext) -> torch.Tensor:
+    """Run the fused GEMM's tile decoder on one 128 x 64 weight tile and return it
+    de-swizzled as a ``[128, 64]`` tensor of *dtype* (rows past ``out_features`` are zero).
+
+    The decoder stores 16-byte chunk ``c`` of tile row ``r`` at chunk position ``c ^ (r & 7)``
+    (the 128-byte swizzle the tensor core reads); this undoes that permutation on the host
+    side so the result can be compared with the dense decode.
+    """
+    ext = _vq_ext(ext)
+    _cabi.require_cuda("vq_decode_tile", packed_indices, centroids, ext.get("residual_indices"),
+                       ext.get("residual_centroids"), ext.get("row_scale"))
+    lib = _cabi.load_library()
+    w = _cabi.vq_struct(packed_indices, centroids, bits, **ext)
+    raw = torch.empty(128 * 128, dtype=torch.uint8, device=packed_indices.device)
+    with torch.cuda.device(packed_indices.device):
+        rc = lib.npb_test_vq_decode_tile(w, out_features, in_features, tile_n, k_block,
+                                         _cabi.dtype_code(dtype), raw.data_ptr(), _cabi.stream_ptr())
+    _cabi.check(rc, "vq_decode_tile")
+    img = raw.view(128, 8, 16)
+    r = torch.arange(128, device=raw.device).view(128, 1)
+    c = torch.arange(8, device=raw.device).view(1, 8)
+    pos = (c ^ (r & 7)).unsqueeze(-1).expand(128, 8, 16)
+    return torch.gather(img, 1, pos).reshape(128, 128).view(dtype)

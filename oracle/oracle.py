@@ -1,0 +1,250 @@
+"""CPU oracle for the quantized-linear forward path.  TEST INFRASTRUCTURE ONLY.
+
+This module restates, on the CPU with numpy (integer / byte work) and torch CPU tensors
+(fp16 / bf16 arithmetic), what the reference computes for the lowered quantized linears.  It
+is the checker for the CUDA kernels: only the tests, the smoke check and the CPU-baseline leg
+of the benchmark may import it.  The library itself never does — it has no CPU path.
+
+Pinned against the reference: ``tests/golden/make_golden.py`` imports the reference's own
+modules and stores their outputs for small seeded cases; ``tests/test_oracle_golden.py`` checks
+every function here against those files, and against the one literal known-answer byte of the
+reference's tests.  The residual-codebook, row-scale and per-column-group codebook forms do
+not exist in the reference: for those the parity is unpinned, and the arithmetic below is
+composed of reference primitives only (unpack, ``centroids[indices]``, ``.to(dtype)``,
+``F.linear``) with fp16 add / multiply rounding once per operation.
+
+Reference locations restated here (paths inside the reference project):
+  * index bit-stream            neuropress/transforms/vq_packing.py:135-295
+  * VQ decode + linear          neuropress/nn/np_vq_linear.py:178-211, 1060-1095
+                                neuropress/kernels/vq_dequant.cu:27-83
+  * nibble unpack               neuropress/nn/np_linear.py:78-96
+  * group-affine decode+linear  neuropress/nn/np_linear.py:298-353
+                                neuropress/kernels/q4_linear.cu:80-131
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+# --------------------------------------------------------------------------------------
+# Index bit-stream
+# --------------------------------------------------------------------------------------
+
+
+def pack_indices(indices: np.ndarray, bits: int) -> np.ndarray:
+    """LSB-first bit-stream pack: index i occupies bits [i*bits, (i+1)*bits).
+
+    Follows ``IndexPacking.pack`` / ``_pack_bitstream`` (vq_packing.py:135-252): one pass per
+    bit, each bit OR-ed into its byte.
+    """
+    if not 4 <= bits <= 20:
+        raise ValueError(f"bits must be in [4, 20], got {bits}.")
+    flat = np.asarray(indices, dtype=np.int64).reshape(-1)
+    n = flat.size
+    if bits == 4 and n % 2:
+        raise ValueError("4-bit packing needs an even index count.")
+    n_bytes = (n * bits + 7) // 8
+    out = np.zeros(n_bytes, dtype=np.uint8)
+    i = np.arange(n, dtype=np.int64)
+    for b in range(bits):
+        pos = i * bits + b
+        bit = ((flat >> b) & 1).astype(np.uint8)
+        np.bitwise_or.at(out, pos >> 3, bit << (pos & 7).astype(np.uint8))
+    return out
+
+
+def unpack_indices_bitloop(packed: np.ndarray, bits: int, n_indices: int) -> np.ndarray:
+    """Faithful restatement of the reference's CPU unpack (vq_packing.py:178-208, 284-295):
+    8-bit is a cast, 4-bit splits nibbles, every other width gathers one bit per pass."""
+    if not 4 <= bits <= 20:
+        raise ValueError(f"bits must be in [4, 20], got {bits}.")
+    p = np.asarray(packed, dtype=np.uint8).reshape(-1)
+    if bits == 8:
+        return p[:n_indices].astype(np.int64)
+    if bits == 4:
+        lo = (p & 0xF).astype(np.int64)
+        hi = (p >> 4).astype(np.int64)
+        return np.stack([lo, hi], axis=1).reshape(-1)[:n_indices]
+    p64 = p.astype(np.int64)
+    i = np.arange(n_indices, dtype=np.int64)
+    out = np.zeros(n_indices, dtype=np.int64)
+    for b in range(bits):
+        pos = i * bits + b
+        out |= ((p64[pos >> 3] >> (pos & 7)) & 1) << b
+    return out
+
+
+def unpack_indices(packed: np.ndarray, bits: int, n_indices: int) -> np.ndarray:
+    """Same result as :func:`unpack_indices_bitloop`, one pass: read the (at most three)
+    bytes that hold an index, shift, mask — the window read of vq_dequant.cu:27-36."""
+    if not 4 <= bits <= 20:
+        raise ValueError(f"bits must be in [4, 20], got {bits}.")
+    p = np.asarray(packed, dtype=np.uint8).reshape(-1)
+    if bits == 8:
+        return p[:n_indices].astype(np.int64)
+    if bits == 16 and p.size >= 2 * n_indices:
+        return p[: 2 * n_indices].view("<u2").astype(np.int64)
+    p64 = np.concatenate([p.astype(np.int64), np.zeros(4, dtype=np.int64)])
+    pos = np.arange(n_indices, dtype=np.int64) * bits
+    b0 = pos >> 3
+    win = p64[b0] | (p64[b0 + 1] << 8) | (p64[b0 + 2] << 16) | (p64[b0 + 3] << 24)
+    return (win >> (pos & 7)) & ((1 << bits) - 1)
+
+
+# --------------------------------------------------------------------------------------
+# VQ decode and forward
+# --------------------------------------------------------------------------------------
+
+
+def _as_np_u8(t) -> np.ndarray:
+    if isinstance(t, torch.Tensor):
+        return t.detach().cpu().contiguous().numpy()
+    return np.asarray(t, dtype=np.uint8)
+
+
+def vq_decode(
+    packed,
+    centroids: torch.Tensor,
+    bits: int,
+    out_features: int,
+    in_features: int,
+    dtype: torch.dtype,
+    *,
+    residual_indices=None,
+    residual_centroids: torch.Tensor | None = None,
+    residual_bits: int = 8,
+    row_scale: torch.Tensor | None = None,
+    cols_per_codebook: int = 0,
+    unpack=unpack_indices,
+) -> torch.Tensor:
+    """Dense weight ``[out_features, in_features]`` in *dtype*.
+
+    Base form (np_vq_linear.py:1091-1095, vq_dequant.cu:50-83):
+        ``W = centroids[unpack(packed)].reshape(N, K).to(dtype)``  with fp16 centroids.
+    Extensions (not in the reference): per-column-group codebooks
+    (``centroids`` is ``[n_cb, NC, VL]``, group ``g`` uses codebook ``g*VL // cols_per_codebook``),
+    a residual codebook added in fp16, a per-output-row fp16 scale multiplied in fp16.
+    """
+    c = centroids.detach().cpu().to(torch.float16)
+    vl = c.shape[-1]
+    N, K = out_features, in_features
+    if K % vl:
+        raise ValueError("in_features must be a multiple of the vector length.")
+    G = K // vl
+    idx = torch.from_numpy(unpack(_as_np_u8(packed), bits, N * G)).reshape(N, G)
+    if cols_per_codebook:
+        if c.dim() != 3:
+            raise ValueError("column-group codebooks need [n_cb, NC, VL] centroids.")
+        cb = (torch.arange(G) * vl) // cols_per_codebook
+        w16 = c[cb.unsqueeze(0).expand(N, G), idx]
+    else:
+        w16 = c[idx]
+    if residual_indices is not None:
+        r = residual_centroids.detach().cpu().to(torch.float16)
+        ridx = torch.from_numpy(unpack(_as_np_u8(residual_indices), residual_bits, N * G)).reshape(N, G)
+        w16 = w16 + r[ridx]  # fp16 add, one rounding
+    w16 = w16.reshape(N, K)
+    if row_scale is not None:
+        w16 = w16 * row_scale.detach().cpu().to(torch.float16).reshape(N, 1)  # fp16 multiply
+    return w16.to(dtype)
+
+
+def vq_forward(x: torch.Tensor, packed, centroids, bits, out_features, in_features,
+               bias: torch.Tensor | None = None, **ext) -> torch.Tensor:
+    """``F.linear(x, decode(...).to(x.dtype), bias)`` — the reference's default / dense path
+    (np_vq_linear.py:1091-1095, 1127-1148)."""
+    x = x.detach().cpu()
+    w = vq_decode(packed, centroids, bits, out_features, in_features, x.dtype, **ext)
+    b = None if bias is None else bias.detach().cpu().to(x.dtype)
+    return F.linear(x, w, b)
+
+
+def vq_forward_f32(x: torch.Tensor, packed, centroids, bits, out_features, in_features,
+                   bias: torch.Tensor | None = None, **ext) -> torch.Tensor:
+    """High-precision yardstick: the weight exactly as decoded for ``x.dtype``, product and
+    accumulation in fp64.  Used to measure how far a low-precision result is from the truth
+    when checking the ``max|err| <= 1e-2 * RMS`` bound."""
+    x = x.detach().cpu()
+    w = vq_decode(packed, centroids, bits, out_features, in_features, x.dtype, **ext)
+    y = x.double() @ w.double().T
+    if bias is not None:
+        y = y + bias.detach().cpu().double()
+    return y
+
+
+# --------------------------------------------------------------------------------------
+# Group-affine (Q4_0 / HQQ) decode and forward
+# --------------------------------------------------------------------------------------
+
+
+def unpack_codes(codes, nbits: int) -> np.ndarray:
+    """``[N, K*nbits/8]`` uint8 -> ``[N, K]`` uint8; value j of a byte sits at bits
+    [j*nbits, (j+1)*nbits) (np_linear.py:78-96)."""
+    c = _as_np_u8(codes)
+    vpb = 8 // nbits
+    shifts = (np.arange(vpb) * nbits).astype(np.uint8)
+    vals = (c[:, :, None] >> shifts[None, None, :]) & ((1 << nbits) - 1)
+    return vals.reshape(c.shape[0], c.shape[1] * vpb).astype(np.uint8)
+
+
+def pack_codes(values, nbits: int) -> np.ndarray:
+    """Inverse of :func:`unpack_codes` (np_linear.py:99-117)."""
+    v = _as_np_u8(values)
+    vpb = 8 // nbits
+    g = v.reshape(v.shape[0], v.shape[1] // vpb, vpb).astype(np.uint8)
+    out = np.zeros(g.shape[:2], dtype=np.uint8)
+    for i in range(vpb):
+        out |= g[:, :, i] << np.uint8(i * nbits)
+    return out
+
+
+def q_decode(codes, scale: torch.Tensor, zero_point: torch.Tensor | None, nbits: int,
+             group_size: int, dtype: torch.dtype) -> torch.Tensor:
+    """``W = ((q.f32 - zp.f32) * s.f32).to(dtype)``; symmetric zero-point ``2**(nbits-1)``
+    (np_linear.py:334-351)."""
+    vals = torch.from_numpy(unpack_codes(codes, nbits).astype(np.float32))
+    N, K = vals.shape
+    ng = K // group_size
+    v = vals.reshape(N, ng, group_size)
+    s = scale.detach().cpu().to(torch.float32).reshape(N, ng, 1)
+    if zero_point is not None:
+        z = zero_point.detach().cpu().to(torch.float32).reshape(N, ng, 1)
+        w = (v - z) * s
+    else:
+        w = (v - float(1 << (nbits - 1))) * s
+    return w.reshape(N, K).to(dtype)
+
+
+def q_forward(x: torch.Tensor, codes, scale, nbits, group_size, zero_point=None,
+              bias=None) -> torch.Tensor:
+    """``F.linear(x, q_decode(...), bias)`` (np_linear.py:353)."""
+    x = x.detach().cpu()
+    w = q_decode(codes, scale, zero_point, nbits, group_size, x.dtype)
+    b = None if bias is None else bias.detach().cpu().to(x.dtype)
+    return F.linear(x, w, b)
+
+
+def q_forward_f64(x: torch.Tensor, codes, scale, nbits, group_size, zero_point=None,
+                  bias=None) -> torch.Tensor:
+    x = x.detach().cpu()
+    w = q_decode(codes, scale, zero_point, nbits, group_size, x.dtype)
+    y = x.double() @ w.double().T
+    if bias is not None:
+        y = y + bias.detach().cpu().double()
+    return y
+
+
+# --------------------------------------------------------------------------------------
+# Shared error metric
+# --------------------------------------------------------------------------------------
+
+
+def rel_max_err(y: torch.Tensor, y_ref: torch.Tensor) -> float:
+    """``max|y - y_ref| / RMS(y_ref)``: the quantity the output tolerance (1e-2 for bf16) is
+    stated on."""
+    y = y.detach().cpu().double()
+    r = y_ref.detach().cpu().double()
+    rms = float(torch.sqrt(torch.mean(r * r)))
+    return float((y - r).abs().max()) / max(rms, 1e-30)

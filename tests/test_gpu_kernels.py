@@ -1,0 +1,234 @@
+"""GPU parity tests: every kernel, called through the C ABI, against the CPU oracle.
+
+Decode is checked bit-exactly (rtol = atol = 0), as the reference checks its own decode kernel
+(tests/nn/test_np_vq_linear.py:546-562 of the reference).  Forward outputs are checked against
+the oracle evaluated in fp64 on the weight decoded for the activation dtype, with the bound
+max|err| <= 1e-2 * RMS(y_ref) (+ half an ulp of the output dtype).
+"""
+
+import pytest
+import torch
+
+import oracle
+from helpers import assert_output_close
+from neuropress_b200 import kernels
+from neuropress_b200.synthetic import make_activations, make_q_layer, make_vq_layer
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _vq_ext_gpu(layer):
+    return {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in layer.ext().items()}
+
+
+def _decode_gpu(layer, dtype):
+    return kernels.vq_dequant(layer.packed.to(DEV), layer.centroids.to(DEV), layer.bits,
+                              layer.out_features, layer.in_features, dtype, **_vq_ext_gpu(layer))
+
+
+def _decode_ref(layer, dtype):
+    return oracle.vq_decode(layer.packed, layer.centroids, layer.bits, layer.out_features,
+                            layer.in_features, dtype, **layer.ext())
+
+
+# ---------------------------------------------------------------------------- decode ---
+@pytest.mark.parametrize("bits", [4, 5, 8, 10, 12, 14, 15, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("vl", [4, 8])
+def test_vq_decode_bit_exact(bits, dtype, vl):
+    # N = 37: the last index ends mid-byte for odd widths; no padding on the stream.
+    layer = make_vq_layer(37, 64, num_centroids=min(1 << bits, 4096), bits=bits, vector_len=vl,
+                          centroid_std=1.0, seed=bits)
+    out = _decode_gpu(layer, dtype)
+    assert out.dtype == dtype
+    torch.testing.assert_close(out.cpu(), _decode_ref(layer, dtype), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_vq_decode_extended_forms_bit_exact(dtype):
+    layer = make_vq_layer(96, 256, num_centroids=512, bits=16, seed=3, residual_centroids=256,
+                          row_scale=True, cols_per_codebook=128)
+    torch.testing.assert_close(_decode_gpu(layer, dtype).cpu(), _decode_ref(layer, dtype),
+                               rtol=0, atol=0)
+
+
+def test_vq_decode_large_codebook_bit_exact():
+    layer = make_vq_layer(512, 1024, num_centroids=65536, bits=16, seed=5, residual_centroids=256,
+                          row_scale=True)
+    torch.testing.assert_close(_decode_gpu(layer, torch.bfloat16).cpu(),
+                               _decode_ref(layer, torch.bfloat16), rtol=0, atol=0)
+
+
+def test_vq_decode_empty_and_errors():
+    layer = make_vq_layer(8, 64, num_centroids=16, seed=1)
+    out = kernels.vq_dequant(layer.packed.to(DEV)[:0], layer.centroids.to(DEV), 4, 0, 64, torch.float16)
+    assert out.shape == (0, 64)
+    with pytest.raises(RuntimeError, match="shape"):  # stream too short
+        kernels.vq_dequant(layer.packed.to(DEV)[:-1], layer.centroids.to(DEV), 4, 8, 64, torch.float16)
+    with pytest.raises(RuntimeError):  # CPU tensors are refused: no fallback
+        kernels.vq_dequant(layer.packed, layer.centroids, 4, 8, 64, torch.float16)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        kernels.vq_dequant(layer.packed.to(DEV), layer.centroids.to(DEV), 3, 8, 64, torch.float16)
+
+
+@pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128), (False, 8)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_q_decode_bit_exact(asym, gs, dtype):
+    layer = make_q_layer(48, 256, group_size=gs, asym=asym, seed=gs)
+    out = kernels.q_dequant(layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                            None if layer.zero_point is None else layer.zero_point.to(DEV), dtype)
+    ref = oracle.q_decode(layer.codes, layer.scale, layer.zero_point, 4, gs, dtype)
+    torch.testing.assert_close(out.cpu(), ref, rtol=0, atol=0)
+
+
+def test_q_decode_8bit_bit_exact():
+    layer = make_q_layer(16, 128, group_size=32, asym=True, nbits=8, seed=2)
+    out = kernels.q_dequant(layer.codes.to(DEV), layer.scale.to(DEV), 8, 32, layer.zero_point.to(DEV),
+                            torch.bfloat16)
+    ref = oracle.q_decode(layer.codes, layer.scale, layer.zero_point, 8, 32, torch.bfloat16)
+    torch.testing.assert_close(out.cpu(), ref, rtol=0, atol=0)
+
+
+# ------------------------------------------------------------------------------ GEMV ---
+def _vq_forward_ref64(layer, x):
+    return oracle.vq_forward_f32(x, layer.packed, layer.centroids, layer.bits, layer.out_features,
+                                 layer.in_features, layer.bias, **layer.ext())
+
+
+GEMV_CASES = [
+    # (N, K, NC, bits, VL, residual, scale, cols_per_codebook, bias)
+    (2048, 2048, 256, 8, 8, 0, False, 0, False),       # small codebook in smem, byte indices
+    (300, 1024, 4096, 12, 8, 0, False, 0, True),       # 12-bit packed stream
+    (300, 1024, 4096, 16, 8, 0, False, 512, False),    # per-column-group codebooks, 64 KiB total
+    (257, 2048, 65536, 16, 8, 256, True, 0, False),    # large codebook + residual + row scale
+    (24, 64, 1024, 10, 4, 0, False, 0, False),         # VL 4, generic width
+    (24, 96, 16, 4, 8, 0, False, 0, True),             # K not a multiple of 64 -> generic path
+    (64, 8192, 4096, 16, 8, 0, False, 2048, False),    # 4 codebooks = 256 KiB -> gathers from L2
+]
+
+
+@pytest.mark.parametrize("case", GEMV_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows", [1, 2, 5, 8])
+def test_vq_gemv_matches_oracle(case, dtype, rows):
+    N, K, NC, bits, vl, res, scale, cpc, bias = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, vector_len=vl, seed=N + K,
+                          residual_centroids=res, row_scale=scale, cols_per_codebook=cpc, bias=bias)
+    x = make_activations(rows, K, dtype, seed=rows)
+    y = kernels.vq_gemv(x.to(DEV), layer.packed.to(DEV), layer.centroids.to(DEV), bits, N,
+                        None if layer.bias is None else layer.bias.to(DEV), **_vq_ext_gpu(layer))
+    assert y.shape == (rows, N) and y.dtype == dtype
+    assert_output_close(y, _vq_forward_ref64(layer, x), dtype)
+
+
+def test_vq_gemv_rejects_too_many_rows():
+    layer = make_vq_layer(16, 64, num_centroids=16, seed=1)
+    x = make_activations(9, 64, torch.float16).to(DEV)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        kernels.vq_gemv(x, layer.packed.to(DEV), layer.centroids.to(DEV), 4, 16)
+
+
+@pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows", [1, 2, 8])
+@pytest.mark.parametrize("shape", [(320, 1024), (67, 4096), (40, 192)])
+def test_q_gemv_matches_oracle(asym, gs, dtype, rows, shape):
+    N, K = shape
+    if K % gs:
+        pytest.skip("group does not divide K")
+    layer = make_q_layer(N, K, group_size=gs, asym=asym, seed=N, bias=True)
+    x = make_activations(rows, K, dtype, seed=rows)
+    y = kernels.q_gemv(x.to(DEV), layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                       None if layer.zero_point is None else layer.zero_point.to(DEV),
+                       layer.bias.to(DEV))
+    ref = oracle.q_forward_f64(x, layer.codes, layer.scale, 4, gs, layer.zero_point, layer.bias)
+    assert_output_close(y, ref, dtype)
+
+
+# ------------------------------------------------------------------- dense tcgen05 GEMM ---
+@pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 512), (256, 512, 1024),
+                                   (130, 72, 96), (1, 64, 64), (2048, 1024, 512), (300, 14336, 256)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dense_gemm_matches_fp32_reference(shape, dtype):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    b = torch.randn(N, generator=g)
+    y = kernels.gemm(x.to(DEV), w.to(DEV), b.to(DEV))
+    from neuropress_b200 import _cabi
+    assert _cabi.gemm_device_status() == 0
+    ref = x.double() @ w.double().T + b.double()
+    assert_output_close(y, ref, dtype, tol=2e-3)
+
+
+# ----------------------------------------------------------------- tile-decode GEMMs ---
+TILE_CASES = [
+    (256, 512, 4096, 16, 0, False, 0),
+    (200, 1024, 4096, 12, 0, False, 0),
+    (384, 512, 65536, 16, 256, True, 0),
+    (128, 2048, 4096, 16, 0, False, 512),
+    (130, 256, 256, 8, 0, False, 0),
+    (72, 128, 1024, 10, 0, False, 0),
+]
+
+
+@pytest.mark.parametrize("case", TILE_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_vq_tile_decoder_bit_exact(case, dtype):
+    """The decoder warps of the fused GEMM produce exactly the dense decode, tile by tile."""
+    N, K, NC, bits, res, scale, cpc = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K, residual_centroids=res,
+                          row_scale=scale, cols_per_codebook=cpc)
+    ref = _decode_ref(layer, dtype)
+    ref_pad = torch.zeros((N + 127) // 128 * 128, K, dtype=dtype)
+    ref_pad[:N] = ref
+    for tn in {0, (N - 1) // 128}:
+        for kb in {0, K // 64 - 1}:
+            tile = kernels.vq_decode_tile(layer.packed.to(DEV), layer.centroids.to(DEV), bits, N, K,
+                                          tn, kb, dtype, **_vq_ext_gpu(layer))
+            want = ref_pad[tn * 128:(tn + 1) * 128, kb * 64:(kb + 1) * 64]
+            torch.testing.assert_close(tile.cpu(), want, rtol=0, atol=0)
+
+FUSED_CASES = [
+    (256, 512, 4096, 16, 0, False, 0),
+    (200, 1024, 4096, 12, 0, False, 0),
+    (384, 512, 65536, 16, 256, True, 0),
+    (128, 2048, 4096, 16, 0, False, 512),
+    (130, 256, 256, 8, 0, False, 0),
+    (72, 128, 1024, 10, 0, False, 0),
+]
+
+
+@pytest.mark.skip(reason="npb_vq_gemm_fused is switched off: see kernels.VQ_TILE_DECODE_GEMM")
+@pytest.mark.parametrize("case", FUSED_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows", [9, 17, 128, 130, 300, 384])
+def test_vq_gemm_fused_matches_oracle(case, dtype, rows):
+    N, K, NC, bits, res, scale, cpc = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K, residual_centroids=res,
+                          row_scale=scale, cols_per_codebook=cpc, bias=True)
+    x = make_activations(rows, K, dtype, seed=rows)
+    y = kernels.vq_gemm_fused(x.to(DEV), layer.packed.to(DEV), layer.centroids.to(DEV), bits, N,
+                              layer.bias.to(DEV), **_vq_ext_gpu(layer))
+    from neuropress_b200 import _cabi
+    assert _cabi.gemm_device_status() == 0
+    assert_output_close(y, _vq_forward_ref64(layer, x), dtype, tol=2e-3)
+
+
+@pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows", [9, 130, 384])
+@pytest.mark.parametrize("shape", [(200, 1024), (256, 512), (72, 128)])
+def test_q_gemm_fused_matches_oracle(asym, gs, dtype, rows, shape):
+    N, K = shape
+    layer = make_q_layer(N, K, group_size=gs, asym=asym, seed=gs, bias=True)
+    x = make_activations(rows, K, dtype, seed=rows)
+    y = kernels.q_gemm_fused(x.to(DEV), layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                             None if layer.zero_point is None else layer.zero_point.to(DEV),
+                             layer.bias.to(DEV))
+    from neuropress_b200 import _cabi
+    assert _cabi.gemm_device_status() == 0
+    ref = oracle.q_forward_f64(x, layer.codes, layer.scale, 4, gs, layer.zero_point, layer.bias)
+    assert_output_close(y, ref, dtype, tol=2e-3)
