@@ -25,6 +25,26 @@ log = logging.getLogger(__name__)
 
 GEMV_MAX_ROWS = _cabi.GEMV_MAX_ROWS
 
+# Optional observer called as hook(symbol, True) right before and hook(symbol, False) right
+# after each C-ABI launch (the benchmark records CUDA events with it).  None = no overhead.
+_launch_hook = None
+
+
+def set_launch_hook(fn) -> None:
+    """Install (or with ``None`` remove) the launch observer."""
+    global _launch_hook
+    _launch_hook = fn
+
+
+def _launch(symbol: str, fn, *args) -> int:
+    hook = _launch_hook
+    if hook is None:
+        return fn(*args)
+    hook(symbol, True)
+    rc = fn(*args)
+    hook(symbol, False)
+    return rc
+
 # ---------------------------------------------------------------------------
 # Fallback reporting (kept for build-failure reporting only: there is no fallback path)
 # ---------------------------------------------------------------------------
@@ -96,7 +116,7 @@ def vq_dequant(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
     elif out.shape != (out_features, in_features) or out.dtype != dtype or not out.is_contiguous():
         raise RuntimeError("vq_dequant: `out` has the wrong shape, dtype or layout.")
     with torch.cuda.device(packed_indices.device):
-        rc = lib.npb_vq_decode(w, out_features, in_features, out.data_ptr(),
+        rc = _launch("npb_vq_decode", lib.npb_vq_decode, w, out_features, in_features, out.data_ptr(),
                                _cabi.dtype_code(dtype), _cabi.stream_ptr())
     _cabi.check(rc, "vq_dequant")
     return out
@@ -117,7 +137,7 @@ def _vq_call(fn_name: str, x: torch.Tensor, packed: torch.Tensor, centroids: tor
     b = _bias_f32(bias, n, x.device)
     y = torch.empty((m, n), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        rc = getattr(lib, fn_name)(w, x.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
+        rc = _launch(fn_name, getattr(lib, fn_name), w, x.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
                                    None if b is None else b.data_ptr(), y.data_ptr(),
                                    _cabi.stream_ptr())
     _cabi.check(rc, fn_name)
@@ -140,15 +160,39 @@ def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torc
     return _vq_call("npb_vq_gemm_fused", x, packed_indices, centroids, bits, out_features, bias, ext)
 
 
+# The VQ tile-decode GEMM is switched off: on a B200 it raised an illegal memory access that
+# reading has not explained (its decoder is verified bit-exact on its own through
+# ``vq_decode_tile``, and the same GEMM skeleton passes with the 4-bit decoder).  While off,
+# the mid-sized band runs the one-pass decode followed by the dense tensor-core GEMM.
+VQ_TILE_DECODE_GEMM = False
+
+
+def vq_dequant_gemm(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
+                    bits: int, out_features: int | None = None, bias: torch.Tensor | None = None,
+                    **ext) -> torch.Tensor:
+    """One-pass decode to a temporary ``[N, K]`` weight in ``x.dtype``, then the dense
+    tensor-core GEMM (reference: ``_forward_dequant_gemm``, np_vq_linear.py:1127-1148)."""
+    k = x.shape[1]
+    n = out_features if out_features is not None else _infer_n(packed_indices, bits, k,
+                                                                centroids.shape[-1])
+    w = vq_dequant(packed_indices, centroids, bits, n, k, x.dtype, **ext)
+    return gemm(x, w, bias)
+
+
 def vq_linear(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
               vector_len: int, bias: torch.Tensor | None = None, **ext) -> torch.Tensor:
     """Fused VQ linear for any row count (reference: ``vq_linear``, vq_linear.cu:344-424).
-    Up to ``GEMV_MAX_ROWS`` rows run the GEMV; more rows run the tile-decode GEMM."""
+    Up to ``GEMV_MAX_ROWS`` rows run the GEMV; more rows run the tile-decode GEMM (or, while
+    that is switched off, decode + dense GEMM)."""
     if centroids.shape[-1] != vector_len:
         raise RuntimeError("vector_len does not match the codebook.")
     if x.shape[0] <= GEMV_MAX_ROWS:
         return vq_gemv(x, packed_indices, centroids, bits, None, bias, **ext)
-    return vq_gemm_fused(x, packed_indices, centroids, bits, None, bias, **ext)
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("vq_linear: more than 8 rows need fp16 or bf16 activations.")
+    if VQ_TILE_DECODE_GEMM and vector_len == 8 and x.shape[1] % 64 == 0:
+        return vq_gemm_fused(x, packed_indices, centroids, bits, None, bias, **ext)
+    return vq_dequant_gemm(x, packed_indices, centroids, bits, None, bias, **ext)
 
 
 def vq_linear_wmma(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
@@ -179,7 +223,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     b = _bias_f32(bias, n, x.device)
     y = torch.empty((m, n), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        rc = lib.npb_gemm(x.data_ptr(), w.data_ptr(), None if b is None else b.data_ptr(),
+        rc = _launch("npb_gemm", lib.npb_gemm, x.data_ptr(), w.data_ptr(), None if b is None else b.data_ptr(),
                           y.data_ptr(), m, n, k, _cabi.dtype_code(x.dtype), _cabi.stream_ptr())
     _cabi.check(rc, "gemm")
     return y
@@ -214,7 +258,8 @@ def q_dequant(w_pack: torch.Tensor, scale: torch.Tensor, nbits: int, group_size:
     w = _cabi.q_struct(w_pack, scale, zero_point, nbits, group_size)
     out = torch.empty((n, k), dtype=dtype, device=w_pack.device)
     with torch.cuda.device(w_pack.device):
-        rc = lib.npb_q_decode(w, n, k, out.data_ptr(), _cabi.dtype_code(dtype), _cabi.stream_ptr())
+        rc = _launch("npb_q_decode", lib.npb_q_decode, w, n, k, out.data_ptr(), _cabi.dtype_code(dtype),
+                     _cabi.stream_ptr())
     _cabi.check(rc, "q_dequant")
     return out
 
@@ -232,7 +277,7 @@ def _q_call(fn_name, x, w_pack, scale, nbits, group_size, zero_point, bias):
     b = _bias_f32(bias, n, x.device)
     y = torch.empty((m, n), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
-        rc = getattr(lib, fn_name)(w, x2.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
+        rc = _launch(fn_name, getattr(lib, fn_name), w, x2.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
                                    None if b is None else b.data_ptr(), y.data_ptr(),
                                    _cabi.stream_ptr())
     _cabi.check(rc, fn_name)

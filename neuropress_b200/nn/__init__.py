@@ -1,0 +1,12 @@
+"""Quantized linear modules (the reference's ``neuropress.nn`` names for this path)."""
+
+from .backends import (Backend, EmbeddingBackend, LinearBackend, NormBackend, VQBackend,
+                       is_cuda_jit_available)
+from .np_linear import NPLinear, linearize_qtensor_weights
+from .np_vq_linear import NPVQLinear, VQProxy, linearize_vq_weights
+
+__all__ = [
+    "Backend", "EmbeddingBackend", "LinearBackend", "NormBackend", "VQBackend",
+    "is_cuda_jit_available", "NPLinear", "linearize_qtensor_weights", "NPVQLinear", "VQProxy",
+    "linearize_vq_weights",
+]
