@@ -347,14 +347,62 @@ def run_reference(args) -> dict:
     }
 
 
+def run_case(args) -> dict:
+    """One band of the workload alone, a few launches: the command line profiled under ncu
+    (small: two weight copies, one row count)."""
+    from neuropress_b200 import kernels
+    from neuropress_b200.synthetic import make_activations, make_q_layer
+
+    global N_COPIES
+    N_COPIES = 2
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    name, rows = args.case.split(":")
+    rows = int(rows)
+    x = make_activations(rows, K_IN, torch.bfloat16, seed=rows).to(device)
+    if name == "vq":
+        layers, nbytes = build_layers(device, 0, 1)
+        run = lambda i: layers[i % N_COPIES](x)  # noqa: E731
+    elif name in ("q40", "hqq"):
+        from neuropress_b200.nn import NPLinear
+
+        layers = []
+        for c in range(N_COPIES):
+            q = make_q_layer(N_OUT, K_IN, group_size=32 if name == "q40" else 64, asym=name == "hqq", seed=c)
+            nbytes = q.packed_bytes()
+            layers.append(NPLinear(q.codes, q.scale, N_OUT, K_IN, q.group_size, 4,
+                                   "asym" if name == "hqq" else "sym", "auto", zero_point=q.zero_point).to(device))
+        run = lambda i: layers[i % N_COPIES](x)  # noqa: E731
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    timer = KernelTimer()
+    timer.rows = rows
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    kernels.set_launch_hook(timer)
+    for i in range(args.steps):
+        run(i)
+    torch.cuda.synchronize()
+    kernels.set_launch_hook(None)
+    out = {"case": args.case, "launches": args.steps, "packed_bytes": nbytes,
+           "kernels_ms": {sym: round(v, 5) for (sym, _), v in timer.mean_ms().items()}}
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default=None,
+                    help="run one band alone, e.g. vq:1, vq:2048, q40:1, hqq:256 (for profiling)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.case:
+        print(json.dumps(run_case(args)), flush=True)
+        return
     line = run_reference(args) if args.impl == "reference" else run_ours(args)
     if line:
         print(json.dumps(line), flush=True)

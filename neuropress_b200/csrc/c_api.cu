@@ -3,6 +3,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+#include <tuple>
+#include <map>
+
 #include "common.cuh"
 
 namespace npb {
@@ -56,6 +60,25 @@ int max_dynamic_smem() {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+int blocks_per_sm(const void* kernel, int threads, size_t smem, int* per_sm) {
+  static std::mutex mu;
+  static std::map<std::tuple<int, const void*, size_t>, int> cache;
+  int dev = 0;
+  NPB_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  const auto key = std::make_tuple(dev, kernel, smem);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    if (smem > 48 * 1024)
+      NPB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int n = 0;
+    NPB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem));
+    it = cache.emplace(key, n).first;
+  }
+  *per_sm = it->second;
+  return NPB_OK;
 }
 
 int validate_vq(const npb_vq_weight* w, int64_t N, int64_t K) {

@@ -40,6 +40,11 @@ int sm_count();
 // Opt a kernel into a large dynamic shared-memory size; cached by the caller.
 int max_dynamic_smem();
 
+// Resident blocks per SM of `kernel` at (threads, dynamic smem); opts the kernel into the
+// shared-memory size on first use.  Cached per (device, kernel, smem): no runtime queries on
+// the launch path after the first call.
+int blocks_per_sm(const void* kernel, int threads, size_t smem, int* per_sm);
+
 // Host-side validation shared by decode / GEMV / fused GEMM.  Mirrors the checks of
 // vq_dequant.cu:112-127 and vq_linear_wmma.cu:475-506 of the reference.
 int validate_vq(const npb_vq_weight* w, int64_t N, int64_t K);

@@ -13,6 +13,8 @@
 //   sum_k x_k (q_k - zp) s  =  s * (sum_k x_k q_k  -  zp * sum_k x_k)
 // with sum_k x_k over each 8-element chunk precomputed once per CTA.  fp32 accumulation.
 // HBM bytes per call: N*K*nbits/8 + 2*(1 or 2)*N*K/g + activations — pure streaming.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace npb {
@@ -108,104 +110,182 @@ __device__ __forceinline__ void load8f(const T* p, float (&f)[8]) {
   }
 }
 
+// Two fp32 FMAs in one instruction (sm_100 packed-fp32 pipe): d += a * b, component-wise.
+__device__ __forceinline__ void ffma2(float2& d, const float2 a, const float2 b) {
+  uint64_t dd = reinterpret_cast<const uint64_t&>(d);
+  asm("fma.rn.f32x2 %0, %1, %2, %0;"
+      : "+l"(dd)
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  d = reinterpret_cast<const float2&>(dd);
+}
+
+// Eight activations (one swizzled chunk) as four fp32 pairs (x0,x1) (x2,x3) (x4,x5) (x6,x7).
+template <typename T>
+__device__ __forceinline__ void load_x_pairs(const T* p, float2 (&xp)[4]) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)  // bf16 -> fp32 is a 16-bit shift
+      xp[i] = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+  } else if constexpr (std::is_same<T, __half>::value) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xp[i] = __half22float2(h[i]);
+  } else {
+    const float4 a = reinterpret_cast<const float4*>(p)[0];
+    const float4 b = reinterpret_cast<const float4*>(p)[1];
+    xp[0] = make_float2(a.x, a.y); xp[1] = make_float2(a.z, a.w);
+    xp[2] = make_float2(b.x, b.y); xp[3] = make_float2(b.z, b.w);
+  }
+}
+
+// A warp owns ROWS output rows at a time; a lane takes 32 consecutive k (16 bytes of codes,
+// exactly one scale group when group_size % 32 == 0) per step, 1024 k per warp step.
+// Nibble q becomes the fp32 value 128 + q with one byte-permute (byte 0x0q dropped into the
+// top mantissa byte of 128.0f), products run on the packed-fp32 pipe (two FMAs per
+// instruction), and the zero-point / scale are applied once per lane step:
+//   acc += s * (sum_k (128 + q_k) x_k  -  (128 + zp) * sum_k x_k).
 template <typename T, int MT, int ROWS>
 __global__ void __launch_bounds__(kThreads) q4_gemv_kernel(QGemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = a.K;
-  const int chunks = K / 8;
-  T* xs = reinterpret_cast<T*>(smem);                                   // [MT][K]
-  float* xsum = reinterpret_cast<float*>(smem + (size_t)MT * K * sizeof(T));  // [MT][chunks]
+  T* xs = reinterpret_cast<T*>(smem);                                         // [MT][K]
+  float* xsum = reinterpret_cast<float*>(smem + (size_t)MT * K * sizeof(T));  // [MT][K/32]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gs = a.group_size;
+  const int groups = K / gs;
+  const int row_bytes = K / 2;
+  const int ksteps = K / 1024;
+  const int stride = gridDim.x * kWarps * ROWS;
+
+  // One lane step of ROWS rows: 16 bytes of codes, scale and zero-point per row.
+  struct Step { uint4 code[ROWS]; __half s[ROWS]; __half z[ROWS]; };
+  auto load_step = [&](Step& st, int n0, int ks) {
+    const int k0 = ks * 1024 + lane * 32;
+    const int g = k0 / gs;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int n = n0 + r < a.N ? n0 + r : a.N - 1;
+      st.code[r] = __ldg(reinterpret_cast<const uint4*>(a.codes + (size_t)n * row_bytes + k0 / 2));
+      st.s[r] = __ldg(a.scale + (size_t)n * groups + g);
+      st.z[r] = a.zp ? __ldg(a.zp + (size_t)n * groups + g) : __float2half_rn(8.f);
+    }
+  };
+
+  // The first weight loads are issued before the activations are staged, so their HBM
+  // latency overlaps the staging; after that the loop always has the next step in flight.
+  int n0 = (blockIdx.x * kWarps + warp) * ROWS, ks = 0;
+  bool have = n0 < a.N;
+  Step cur;
+  if (have) load_step(cur, n0, 0);
   {
     const T* x = static_cast<const T*>(a.x);
-    for (int t = tid; t < MT * chunks; t += kThreads) {
-      const int m = t / chunks, j = t - m * chunks;
-      T* dst = xs + (size_t)m * K + swz8(j);
+    for (int t = tid; t < MT * (K / 32); t += kThreads) {
+      const int m = t / (K / 32), j4 = t - m * (K / 32);
       float s = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const T v = (m < a.M) ? x[(size_t)m * K + j * 8 + e] : from_f32<T>(0.f);
-        dst[e] = v;
-        s += to_f32(v);
+      for (int c = 0; c < 4; ++c) {
+        const int j = j4 * 4 + c;
+        struct alignas(16) V8 { T v[8]; } v;
+        if (m < a.M) {
+          v = *reinterpret_cast<const V8*>(x + (size_t)m * K + j * 8);  // K % 1024 == 0, x 16 B aligned
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v.v[e] = from_f32<T>(0.f);
+        }
+        *reinterpret_cast<V8*>(xs + (size_t)m * K + swz8(j)) = v;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += to_f32(v.v[e]);
       }
-      xsum[m * chunks + j] = s;
+      xsum[t] = s;
     }
   }
   __syncthreads();
 
-  const int gs = a.group_size;
-  const int groups = K / gs;
-  const int row_bytes = K / 2;
-  const int warps_total = gridDim.x * kWarps;
-  for (int n0 = (blockIdx.x * kWarps + warp) * ROWS; n0 < a.N; n0 += warps_total * ROWS) {
-    float acc[ROWS][MT];
+  float acc[ROWS][MT];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+
+  while (have) {
+    int nn0 = n0, nks = ks + 1;
+    if (nks == ksteps) { nks = 0; nn0 = n0 + stride; }
+    const bool have_next = nn0 < a.N;
+    Step nxt;
+    if (have_next) load_step(nxt, nn0, nks);
+
+    const int k0 = ks * 1024 + lane * 32;
+    float2 d[ROWS][MT];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-      for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
-
-    for (int k0 = lane * 32; k0 < K; k0 += 1024) {
-      uint4 code[ROWS];
-      float sc[ROWS], zo[ROWS];
-      const int g = k0 / gs;  // the lane's 32 values lie inside one group (gs % 32 == 0)
+      for (int m = 0; m < MT; ++m) d[r][m] = make_float2(0.f, 0.f);
+    const int j0 = k0 / 8;
+#pragma unroll
+    for (int ch = 0; ch < 4; ++ch) {
+      float2 xp[MT][4];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) load_x_pairs<T>(xs + (size_t)m * K + swz8(j0 + ch), xp[m]);
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
-        const int n = n0 + r < a.N ? n0 + r : a.N - 1;
-        code[r] = __ldg(reinterpret_cast<const uint4*>(a.codes + (size_t)n * row_bytes + k0 / 2));
-        sc[r] = __half2float(__ldg(a.scale + (size_t)n * groups + g));
-        zo[r] = 128.f + (a.zp ? __half2float(__ldg(a.zp + (size_t)n * groups + g)) : 8.f);
+        const uint32_t word = ch == 0 ? cur.code[r].x : ch == 1 ? cur.code[r].y
+                            : ch == 2 ? cur.code[r].z : cur.code[r].w;
+        const uint32_t lo = word & 0x0f0f0f0fu;          // nibbles 0, 2, 4, 6 (one per byte)
+        const uint32_t hi = (word >> 4) & 0x0f0f0f0fu;   // nibbles 1, 3, 5, 7
+        float2 q[4];
+        q[0] = make_float2(__uint_as_float(__byte_perm(lo, 0x43000000u, 0x7044)),
+                           __uint_as_float(__byte_perm(hi, 0x43000000u, 0x7044)));
+        q[1] = make_float2(__uint_as_float(__byte_perm(lo, 0x43000000u, 0x7144)),
+                           __uint_as_float(__byte_perm(hi, 0x43000000u, 0x7144)));
+        q[2] = make_float2(__uint_as_float(__byte_perm(lo, 0x43000000u, 0x7244)),
+                           __uint_as_float(__byte_perm(hi, 0x43000000u, 0x7244)));
+        q[3] = make_float2(__uint_as_float(__byte_perm(lo, 0x43000000u, 0x7344)),
+                           __uint_as_float(__byte_perm(hi, 0x43000000u, 0x7344)));
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) ffma2(d[r][m], q[i], xp[m][i]);
+        }
       }
-      float d[ROWS][MT];
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const float xs32 = xsum[m * (K / 32) + k0 / 32];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r)
+        acc[r][m] = fmaf(__half2float(cur.s[r]),
+                         (d[r][m].x + d[r][m].y) - (128.f + __half2float(cur.z[r])) * xs32, acc[r][m]);
+    }
+
+    if (ks == ksteps - 1) {  // row group finished: reduce over the warp and write
 #pragma unroll
       for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-        for (int m = 0; m < MT; ++m) d[r][m] = 0.f;
-      const int j0 = k0 / 8;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const int pos = swz8(j0 + ch);
-        float xv[MT][8];
-#pragma unroll
-        for (int m = 0; m < MT; ++m) load8f<T>(xs + (size_t)m * K + pos, xv[m]);
+        for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum(acc[r][m]);
+      if (lane == 0) {
+        T* y = static_cast<T*>(a.y);
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-          const uint32_t word = ch == 0 ? code[r].x : ch == 1 ? code[r].y : ch == 2 ? code[r].z : code[r].w;
+          const int n = n0 + r;
+          if (n >= a.N) continue;
+          const float b = a.bias ? __ldg(a.bias + n) : 0.f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            // fp32 bit pattern of 128 + q: the nibble dropped into the top mantissa bits of
-            // 128.0f (ulp 2^-16 ... bit 16 has weight 1).
-            const uint32_t sh = e <= 4 ? (word << (16 - 4 * e)) : (word >> (4 * e - 16));
-            const float qf = __uint_as_float(0x43000000u | (sh & 0x000f0000u));
-#pragma unroll
-            for (int m = 0; m < MT; ++m) d[r][m] = fmaf(qf, xv[m][e], d[r][m]);
-          }
+          for (int m = 0; m < MT; ++m)
+            if (m < a.M) y[(size_t)m * a.N + n] = from_f32<T>(acc[r][m] + b);
         }
       }
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const float4 s4 = *reinterpret_cast<const float4*>(xsum + m * chunks + j0);
-        const float xs32 = (s4.x + s4.y) + (s4.z + s4.w);
+      for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r)
-          acc[r][m] = fmaf(sc[r], d[r][m] - zo[r] * xs32, acc[r][m]);
-      }
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
     }
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum(acc[r][m]);
-    if (lane == 0) {
-      T* y = static_cast<T*>(a.y);
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        const int n = n0 + r;
-        if (n >= a.N) continue;
-        const float b = a.bias ? __ldg(a.bias + n) : 0.f;
-#pragma unroll
-        for (int m = 0; m < MT; ++m)
-          if (m < a.M) y[(size_t)m * a.N + n] = from_f32<T>(acc[r][m] + b);
-      }
-    }
+    cur = nxt;
+    n0 = nn0;
+    ks = nks;
+    have = have_next;
   }
 }
 
@@ -244,10 +324,8 @@ __global__ void __launch_bounds__(kThreads) q_gemv_generic_kernel(QGemvArgs a) {
 template <typename KernT>
 int launch_persistent(KernT kern, const QGemvArgs& a, size_t smem, int rows_per_warp,
                       cudaStream_t st) {
-  if (smem > 48 * 1024)
-    NPB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
-  NPB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
+  if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), kThreads, smem, &per_sm)) return rc;
   if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
   const int rows_per_block = kWarps * rows_per_warp;
   const int want = (a.N + rows_per_block - 1) / rows_per_block;
@@ -260,14 +338,14 @@ int launch_persistent(KernT kern, const QGemvArgs& a, size_t smem, int rows_per_
 template <typename T>
 int run_gemv(const npb_q_weight* w, QGemvArgs a, cudaStream_t st) {
   const bool fast = w->nbits == 4 && a.K % 1024 == 0 && w->group_size % 32 == 0 &&
-                    aligned_to(a.codes, 16);
+                    aligned_to(a.codes, 16) && aligned_to(a.x, 16);
   if (!fast) {
     if (w->nbits == 4) return launch_persistent(q_gemv_generic_kernel<T, 4>, a, 0, 1, st);
     return launch_persistent(q_gemv_generic_kernel<T, 8>, a, 0, 1, st);
   }
   const int M = a.M;
   int batch = 8;
-  auto need = [&](int mt) { return (size_t)mt * a.K * sizeof(T) + (size_t)mt * (a.K / 8) * 4; };
+  auto need = [&](int mt) { return (size_t)mt * a.K * sizeof(T) + (size_t)mt * (a.K / 32) * 4; };
   while (batch > 1 && need(batch) > (size_t)max_dynamic_smem() / 2) batch >>= 1;
   if (need(batch) > (size_t)max_dynamic_smem()) return NPB_ERR_TOO_LARGE;
   for (int m0 = 0; m0 < M; m0 += batch) {
@@ -278,7 +356,7 @@ int run_gemv(const npb_q_weight* w, QGemvArgs a, cudaStream_t st) {
     const int mt = b.M <= 1 ? 1 : b.M <= 2 ? 2 : b.M <= 4 ? 4 : 8;
     int rc;
     switch (mt) {
-      case 1: rc = launch_persistent(q4_gemv_kernel<T, 1, 2>, b, need(1), 2, st); break;
+      case 1: rc = launch_persistent(q4_gemv_kernel<T, 1, 4>, b, need(1), 4, st); break;
       case 2: rc = launch_persistent(q4_gemv_kernel<T, 2, 2>, b, need(2), 2, st); break;
       case 4: rc = launch_persistent(q4_gemv_kernel<T, 4, 1>, b, need(4), 1, st); break;
       default: rc = launch_persistent(q4_gemv_kernel<T, 8, 1>, b, need(8), 1, st); break;

@@ -208,9 +208,8 @@ __global__ void __launch_bounds__(kThreads) vq_gemv_kernel(GemvArgs a) {
 template <typename T, int VL, int BITS, int MT, bool CB_SMEM>
 int launch(const GemvArgs& a, size_t smem, cudaStream_t st) {
   auto kern = vq_gemv_kernel<T, VL, BITS, MT, CB_SMEM>;
-  NPB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
-  NPB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
+  if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), kThreads, smem, &per_sm)) return rc;
   if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
   const int want = (a.N + kWarps - 1) / kWarps;
   const int grid = want < sm_count() * per_sm ? want : sm_count() * per_sm;
