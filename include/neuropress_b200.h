@@ -132,6 +132,35 @@ int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_
 int npb_q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
                      int64_t K, const float* bias, void* y, npb_stream_t stream);
 
+/* Size of the scratch array built into the library for npb_vq_linear_static_scratch: 32 MiB,
+ * i.e. weights of up to 16,777,216 elements (4096 x 4096) in bf16 / fp16. */
+#define NPB_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+
+/*
+ * y[M, N] = x[M, K] . W^T (+ bias) by one-pass decode + dense tensor-core GEMM, for callers
+ * that cannot allocate device memory.  It has no counterpart in the reference, which always
+ * takes its temporary weight from torch's allocator.
+ *
+ * Who needs it: a host that only owns the buffers it was given (a plain C / C++ service with a
+ * fixed memory budget, a plugin loaded into someone else's process), or a latency-critical
+ * loop where cudaMalloc is off limits because it synchronises the device and may fail when
+ * memory is tight.  The dense temporary weight lives in an array of NPB_STATIC_SCRATCH_BYTES
+ * inside the library, so the call allocates nothing - not with cudaMalloc, not through any
+ * library.  The price is that every GPU that loads the library gives up that much memory
+ * until the process ends.
+ *
+ * Rules:  N * K * 2 bytes must fit in the array, otherwise NPB_ERR_TOO_LARGE is returned and
+ * nothing is launched.  x / y are NPB_BF16 or NPB_F16, K % 8 == 0, bias fp32 or NULL; inputs
+ * and outputs are still the caller's.  All calls share the one array: order them on a single
+ * stream - calls that overlap on the GPU corrupt each other's weights.  The array never needs
+ * clearing (each call overwrites the part it reads).  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress) and sets kernel attributes; make that
+ * first call outside of any stream capture.
+ */
+int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
+                                 int64_t N, int64_t K, const float* bias, void* y,
+                                 npb_stream_t stream);
+
 /* Test hook, no reference counterpart: runs the tile decoder of npb_vq_gemm_fused on one
  * 128-row x 64-column W tile (rows [128*tile_n, +128), columns [64*k_block, +64)) and writes
  * the 16 KiB shared-memory image to out: row r occupies bytes [128 r, 128 r + 128), its

@@ -19,6 +19,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libneuropress_b200.so"
 
 NPB_F16, NPB_BF16, NPB_F32 = 0, 1, 2
 GEMV_MAX_ROWS = 8
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 _DTYPE_CODE = {torch.float16: NPB_F16, torch.bfloat16: NPB_BF16, torch.float32: NPB_F32}
 
@@ -35,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "npb_gemm",
     "npb_vq_gemm_fused",
     "npb_q_gemm_fused",
+    "npb_vq_linear_static_scratch",
     "npb_test_vq_decode_tile",
     "npb_gemm_device_status",
 )
@@ -104,6 +106,7 @@ def load_library() -> ctypes.CDLL:
     lib.npb_vq_gemv.argtypes = [vq_p, *gemv_tail]
     lib.npb_q_gemv.argtypes = [q_p, *gemv_tail]
     lib.npb_vq_gemm_fused.argtypes = [vq_p, *gemv_tail]
+    lib.npb_vq_linear_static_scratch.argtypes = [vq_p, *gemv_tail]
     lib.npb_q_gemm_fused.argtypes = [q_p, *gemv_tail]
     lib.npb_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                              c_int, c_void_p]

@@ -29,6 +29,7 @@ SOURCES = [
     "vq_gemv.cu",
     "q_kernels.cu",
     "gemm_tcgen05.cu",
+    "static_scratch.cu",
 ]
 
 NVCC_FLAGS = [

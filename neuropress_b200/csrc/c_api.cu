@@ -26,6 +26,8 @@ int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_
                  void*, cudaStream_t);
 
 int gemm_device_status(int*);
+int vq_linear_static_scratch(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t,
+                             const float*, void*, cudaStream_t);
 int vq_decode_tile_probe(const npb_vq_weight*, int64_t, int64_t, int, int, int, void*, cudaStream_t);
 
 static thread_local char g_last_error[256] = "";
@@ -133,7 +135,7 @@ const char* npb_status_string(int status) {
     case NPB_ERR_SHAPE: return "inconsistent shape (K % vector_len, group size, or packed buffer too short)";
     case NPB_ERR_ALIGNMENT: return "pointer not aligned as required";
     case NPB_ERR_CUDA: return "CUDA call failed (see npb_last_cuda_error)";
-    case NPB_ERR_TOO_LARGE: return "size exceeds a fixed capacity";
+    case NPB_ERR_TOO_LARGE: return "size exceeds a fixed capacity (the built-in scratch array or shared memory)";
     case NPB_ERR_DEVICE_TIMEOUT: return "a bounded in-kernel wait gave up";
     default: return "unknown status";
   }
@@ -182,6 +184,13 @@ int npb_test_vq_decode_tile(const npb_vq_weight* w, int64_t N, int64_t K, int ti
                             int dtype, void* out, npb_stream_t stream) {
   return npb::vq_decode_tile_probe(w, N, K, tile_n, k_block, dtype, out,
                                    static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
+                                 int64_t N, int64_t K, const float* bias, void* y,
+                                 npb_stream_t stream) {
+  return npb::vq_linear_static_scratch(w, x, x_dtype, M, N, K, bias, y,
+                                       static_cast<cudaStream_t>(stream));
 }
 
 int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }
