@@ -207,9 +207,34 @@ def run_ours(args) -> dict:
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
+        # NCCL prints its version banner on stdout at the first collective; stdout carries
+        # exactly one JSON line, so stdout is pointed at stderr until the group is up.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     layers, packed_bytes = build_layers(device, rank, world)
+    gather_kind = "none"
+    if world > 1:
+        gather_kind = "NCCL all-gather + re-layout copy"
+        if not args.nccl_gather:
+            try:
+                from neuropress_b200.sharding import PushGather
+
+                shared = PushGather(None, max(ROWS), N_OUT, torch.bfloat16, device)
+                for layer in layers:
+                    layer.push = shared
+                gather_kind = "peer-store push (npb_allgather_push)"
+            except Exception as exc:  # symmetric memory unavailable: keep NCCL
+                print(f"[bench] push gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
     xs_host = {m: make_activations(m, K_IN, torch.bfloat16, seed=m).pin_memory() for m in ROWS}
     xs = {m: xs_host[m].to(device) for m in ROWS}
     ys_host = {m: torch.empty((m, N_OUT), dtype=torch.bfloat16).pin_memory() for m in ROWS}
@@ -323,7 +348,7 @@ def run_ours(args) -> dict:
                                + "/".join(map(str, ROWS)),
                    "tokens_per_step": tokens_per_step,
                    "l2": f"cold: {N_COPIES} weight copies ({N_COPIES * packed_bytes / 1e6:.0f} MB) rotated per forward",
-                   "parallelism": "single GPU" if world == 1 else f"out-feature shards x{world} + NCCL all-gather"},
+                   "parallelism": "single GPU" if world == 1 else f"out-feature shards x{world} + {gather_kind}"},
         "e2e": {"value": round(tokens_per_step * args.steps / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": tokens_per_step * K_IN * 2,
                 "d2h_bytes_per_step": tokens_per_step * N_OUT * 2,
@@ -404,12 +429,12 @@ def run_reference(args) -> dict:
 
 def run_case(args) -> dict:
     """One band of the workload alone, a few launches: the command line profiled under ncu
-    (small: two weight copies, one row count)."""
+    (small: four weight copies, one row count)."""
     from neuropress_b200 import kernels
     from neuropress_b200.synthetic import make_activations, make_q_layer
 
     global N_COPIES
-    N_COPIES = 2
+    N_COPIES = 4
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
     name, rows = args.case.split(":")
@@ -442,6 +467,32 @@ def run_case(args) -> dict:
     kernels.set_launch_hook(None)
     out = {"case": args.case, "launches": args.steps, "packed_bytes": nbytes,
            "kernels_ms": {sym: round(v, 5) for (sym, _), v in timer.mean_ms().items()}}
+    # The event pairs above include the host's enqueue latency when a kernel is shorter than a
+    # Python call.  Replaying the same forwards from a CUDA graph removes the host from the
+    # timed region: this is the device time per forward.
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(2):
+                run(i)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(args.steps):
+                    run(i)
+            graph.replay()
+            side.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(side)
+            graph.replay()
+            t1.record(side)
+            side.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        out["graph_ms_per_forward"] = round(ms, 5)
+        out["graph_packed_GBps"] = round(nbytes / (ms * 1e-3) / 1e9, 1)
+        out["graph_TFLOPs"] = round(2.0 * rows * N_OUT * K_IN / (ms * 1e-3) / 1e12, 2)
+    except Exception as exc:  # graph capture is a measurement aid only
+        out["graph_error"] = repr(exc)[:200]
     return out
 
 
@@ -454,6 +505,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="N > 1: all-gather with NCCL instead of the peer-store push kernel")
     args = ap.parse_args()
     if args.case:
         print(json.dumps(run_case(args)), flush=True)

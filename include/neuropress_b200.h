@@ -161,6 +161,21 @@ int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dt
                                  int64_t N, int64_t K, const float* bias, void* y,
                                  npb_stream_t stream);
 
+/*
+ * Multi-GPU (new; the reference has no distributed code): all-gather of out-feature shards by
+ * pushing.  This rank's src[M, n_local] (elem_bytes per element) is stored into columns
+ * [rank*n_local, (rank+1)*n_local) of EVERY rank's [M, n_local*world] buffer; then each rank
+ * flags every peer and waits (at most 2 s) for all peers' flags, so when the kernel ends the
+ * local buffer holds the full [M, N].  peer_out / peer_flags are DEVICE arrays of `world`
+ * pointers (symmetric-memory buffer addresses of ranks 0..world-1); each rank's flag buffer
+ * holds world + 2 zero-initialised uint32 words (per-peer epochs, a counter, a status word
+ * that becomes 1 if a wait gave up).  epoch must increase by one per call on all ranks.
+ * n_local * elem_bytes must be a multiple of 16.  One rank per GPU.
+ */
+int npb_allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem_bytes,
+                       const void* peer_out, const void* peer_flags, int rank, int world,
+                       uint32_t epoch, npb_stream_t stream);
+
 /* Test hook, no reference counterpart: runs the tile decoder of npb_vq_gemm_fused on one
  * 128-row x 64-column W tile (rows [128*tile_n, +128), columns [64*k_block, +64)) and writes
  * the 16 KiB shared-memory image to out: row r occupies bytes [128 r, 128 r + 128), its

@@ -37,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "npb_vq_gemm_fused",
     "npb_q_gemm_fused",
     "npb_vq_linear_static_scratch",
+    "npb_allgather_push",
     "npb_test_vq_decode_tile",
     "npb_gemm_device_status",
 )
@@ -112,6 +113,8 @@ def load_library() -> ctypes.CDLL:
                              c_int, c_void_p]
     lib.npb_test_vq_decode_tile.argtypes = [vq_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p,
                                             c_void_p]
+    lib.npb_allgather_push.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int,
+                                       c_int, ctypes.c_uint32, c_void_p]
     lib.npb_gemm_device_status.argtypes = [POINTER(c_int)]
     for name in EXPORTED_SYMBOLS[3:]:
         getattr(lib, name).restype = c_int

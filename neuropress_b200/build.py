@@ -28,8 +28,10 @@ SOURCES = [
     "vq_decode.cu",
     "vq_gemv.cu",
     "q_kernels.cu",
+    "q_gemv_mma.cu",
     "gemm_tcgen05.cu",
     "static_scratch.cu",
+    "allgather_push.cu",
 ]
 
 NVCC_FLAGS = [

@@ -26,6 +26,8 @@ int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_
                  void*, cudaStream_t);
 
 int gemm_device_status(int*);
+int allgather_push(const void*, int64_t, int64_t, int64_t, const void*, const void*, int, int, uint32_t,
+                   cudaStream_t);
 int vq_linear_static_scratch(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t,
                              const float*, void*, cudaStream_t);
 int vq_decode_tile_probe(const npb_vq_weight*, int64_t, int64_t, int, int, int, void*, cudaStream_t);
@@ -191,6 +193,13 @@ int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dt
                                  npb_stream_t stream) {
   return npb::vq_linear_static_scratch(w, x, x_dtype, M, N, K, bias, y,
                                        static_cast<cudaStream_t>(stream));
+}
+
+int npb_allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem_bytes,
+                       const void* peer_out, const void* peer_flags, int rank, int world,
+                       uint32_t epoch, npb_stream_t stream) {
+  return npb::allgather_push(src, M, n_local, elem_bytes, peer_out, peer_flags, rank, world, epoch,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }

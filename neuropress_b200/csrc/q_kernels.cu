@@ -18,6 +18,10 @@
 #include "common.cuh"
 
 namespace npb {
+
+int q4_gemv_mma(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
+                void*, cudaStream_t);
+
 namespace {
 
 // ------------------------------------------------------------------ decode ------------
@@ -397,6 +401,11 @@ int q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t
   a.x = x;
   a.y = y;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.group_size = w->group_size;
+  {
+    // Tensor-core GEMV first (bf16 / fp16, K % 512 == 0); it declines other shapes.
+    const int rc = q4_gemv_mma(w, x, x_dtype, M, N, K, bias, y, st);
+    if (rc != NPB_ERR_UNSUPPORTED) return rc;
+  }
   switch (x_dtype) {
     case NPB_BF16: return run_gemv<__nv_bfloat16>(w, a, st);
     case NPB_F16: return run_gemv<__half>(w, a, st);

@@ -91,6 +91,67 @@ def gather_outputs(y_local: torch.Tensor, group: dist.ProcessGroup | None = None
     return out.reshape(*leading, world * n_local)
 
 
+class PushGather:
+    """All-gather of ``[M, N/P]`` shard outputs by peer stores into symmetric memory.
+
+    Replaces the NCCL all-gather + re-layout copy by one small kernel of this library
+    (``npb_allgather_push``): each rank writes its slice into every rank's ``[M, N]`` buffer over
+    NVLink, then flags its peers and waits (bounded) for theirs.  Two output buffers alternate,
+    so the tensor returned by a call stays valid until the call after the next one; consumers
+    must run on the same stream before that.  Needs one rank per GPU and peer access between
+    them (``torch.distributed._symmetric_memory``); construction is collective.
+    """
+
+    def __init__(self, group: dist.ProcessGroup | None, max_rows: int, n_full: int,
+                 dtype: torch.dtype, device: torch.device) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        grp = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(grp)
+        self.rank = dist.get_rank(grp)
+        if n_full % self.world:
+            raise ValueError("n_full must be divisible by the world size.")
+        self.n_full, self.max_rows, self.dtype = n_full, max_rows, dtype
+        self.n_local = n_full // self.world
+        if (self.n_local * dtype.itemsize) % 16:
+            raise ValueError("a shard row must be a multiple of 16 bytes.")
+        self.bufs, self.handles = [], []
+        for _ in range(2):
+            b = symm_mem.empty((max_rows, n_full), dtype=dtype, device=device)
+            self.bufs.append(b)
+            self.handles.append(symm_mem.rendezvous(b, grp))
+        self.flags = symm_mem.empty(self.world + 2 + 62, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flags_handle = symm_mem.rendezvous(self.flags, grp)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)
+        self.epoch = 0
+
+    def __call__(self, y_local: torch.Tensor) -> torch.Tensor:
+        from . import _cabi
+        from .kernels import _launch
+
+        *leading, n_local = y_local.shape
+        flat = y_local.reshape(-1, n_local).contiguous()
+        m = flat.shape[0]
+        if n_local != self.n_local or flat.dtype != self.dtype or m > self.max_rows:
+            raise RuntimeError("PushGather: shard shape / dtype / row count outside what it was built for.")
+        self.epoch += 1
+        which = self.epoch & 1
+        lib = _cabi.load_library()
+        with torch.cuda.device(flat.device):
+            rc = _launch("npb_allgather_push", lib.npb_allgather_push, flat.data_ptr(), m, n_local,
+                         flat.dtype.itemsize, self.handles[which].buffer_ptrs_dev,
+                         self.flags_handle.buffer_ptrs_dev, self.rank, self.world, self.epoch,
+                         _cabi.stream_ptr())
+        _cabi.check(rc, "npb_allgather_push")
+        return self.bufs[which][:m].reshape(*leading, self.n_full)
+
+    def status(self) -> int:
+        """Synchronise and return the status word (1 = a bounded wait gave up)."""
+        return int(self.flags[self.world + 1].item())
+
+
 class ShardedLinear(nn.Module):
     """A rank's shard of a quantized linear plus the all-gather of the outputs.
 
@@ -121,9 +182,18 @@ class ShardedLinear(nn.Module):
             raise TypeError(f"cannot shard a {type(layer).__name__}.")
         return cls(local, layer.out_features, rank, world_size, group, gather)
 
+    def enable_push_gather(self, max_rows: int, dtype: torch.dtype, device: torch.device) -> None:
+        """Collective: switch the all-gather from NCCL to peer stores (:class:`PushGather`)."""
+        self.push = PushGather(self.group, max_rows, self.out_features, dtype, device)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self.local(x)
-        return gather_outputs(y, self.group) if self.gather else y
+        if not self.gather:
+            return y
+        push = getattr(self, "push", None)
+        if push is not None and y.dtype == push.dtype and y.numel() // y.shape[-1] <= push.max_rows:
+            return push(y)
+        return gather_outputs(y, self.group)
 
     def extra_repr(self) -> str:
         return f"rank={self.rank}/{self.world_size}, out={self.out_features}, gather={self.gather}"

@@ -1,0 +1,90 @@
+"""Two-GPU test of the sharded linear: out-feature shards + all-gather, both over NCCL and by
+peer stores (``npb_allgather_push``).  Runs only where two CUDA devices are visible; one child
+process per GPU."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, q) -> None:
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    for p in (root, root / "oracle", root / "tests"):
+        sys.path.insert(0, str(p))
+    import torch.distributed as dist
+
+    import oracle
+    from helpers import assert_output_close
+    from neuropress_b200.nn import NPVQLinear, VQProxy
+    from neuropress_b200.sharding import ShardedLinear
+    from neuropress_b200.synthetic import make_activations, make_vq_layer
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    ok, msg = True, ""
+    try:
+        d = make_vq_layer(512, 1024, num_centroids=65536, bits=16, seed=3, residual_centroids=256,
+                          row_scale=True, bias=True)
+        full = NPVQLinear(VQProxy(d.centroids), d.packed, 16, 512, 1024, 8, backend="auto", bias=d.bias,
+                          residual_proxy=VQProxy(d.residual_centroids), residual_indices=d.residual_indices,
+                          row_scale=d.row_scale)
+        layer = ShardedLinear.from_layer(full, rank, world)
+        layer.local.proxy.to(dev)
+        layer.local.residual_proxy.to(dev)
+        layer.to(dev)
+        refs = {}
+        for rows in (1, 2, 16, 300):
+            x = make_activations(rows, 1024, torch.bfloat16, seed=rows)
+            refs[rows] = (x.to(dev), oracle.vq_forward_f32(x, d.packed, d.centroids, 16, 512, 1024, d.bias,
+                                                           **d.ext()))
+        for rows, (x, ref) in refs.items():           # NCCL all-gather
+            y = layer(x)
+            assert y.shape == (rows, 512)
+            assert_output_close(y, ref, torch.bfloat16)
+        layer.enable_push_gather(max_rows=300, dtype=torch.bfloat16, device=dev)
+        for it in range(3):                           # push gather, buffers alternate
+            for rows, (x, ref) in refs.items():
+                y = layer(x)
+                assert y.shape == (rows, 512)
+                assert_output_close(y, ref, torch.bfloat16)
+        assert layer.push.status() == 0
+    except Exception as exc:  # report instead of hanging the peer
+        ok, msg = False, repr(exc)[:500]
+    finally:
+        q.put((rank, ok, msg))
+        try:
+            dist.barrier()
+        except Exception:
+            pass
+        dist.destroy_process_group()
+
+
+def test_sharded_linear_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(timeout=120)
+    assert results == [(0, True, ""), (1, True, "")], results
