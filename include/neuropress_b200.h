@@ -180,7 +180,9 @@ int npb_allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem
  * 128-row x 64-column W tile (rows [128*tile_n, +128), columns [64*k_block, +64)) and writes
  * the 16 KiB shared-memory image to out: row r occupies bytes [128 r, 128 r + 128), its
  * 16-byte chunk c is stored at chunk position c ^ (r & 7) (the 128-byte swizzle the tensor
- * core reads); rows past N are zero.  dtype NPB_BF16 or NPB_F16. */
+ * core reads); rows past N are zero.  dtype NPB_BF16 or NPB_F16.  k_block == -1 decodes every
+ * K block of the tile through the GEMM's shared-memory ring under its thread geometry and
+ * writes K/64 consecutive 16 KiB images. */
 int npb_test_vq_decode_tile(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
                             int dtype, void* out, npb_stream_t stream);
 

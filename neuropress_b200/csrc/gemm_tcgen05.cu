@@ -56,6 +56,10 @@ struct FusedVq {
   const __half* row_scale;
   int bits, res_bits, num_centroids, groups_per_codebook;
   int cb_rows, res_rows;  // total codebook rows (n_codebooks * num_centroids), residual rows
+  // Whether the optional parts exist.  The pointers above are never null: an absent part
+  // aliases the main stream / codebook (see fill_fused_vq), so a load the compiler hoists
+  // above the test of these flags still reads mapped memory.
+  int has_res, has_scale;
 };
 
 struct FusedQ4 {
@@ -130,7 +134,9 @@ __device__ __forceinline__ void decode_vq_row(const FusedVq& p, int n, int N, in
     return;
   }
   uint32_t idx[8], ridx[8];
-  const bool has_res = p.res_packed != nullptr;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) ridx[c] = 0;
+  const bool has_res = p.has_res != 0;
   if constexpr (BITS != 0) {
     const int64_t chunk = (int64_t)n * (G >> 3) + kb;
     // The decoder checks its own accesses: a stream offset or codebook index outside the
@@ -168,8 +174,8 @@ __device__ __forceinline__ void decode_vq_row(const FusedVq& p, int n, int N, in
 #pragma unroll
   for (int c = 0; c < 8; ++c) cv[c] = ldg_vec(reinterpret_cast<const Half8*>(p.centroids) + idx[c]);
   __half2 s2 = __float2half2_rn(1.f);
-  const bool has_scale = p.row_scale != nullptr;
-  if (has_scale) s2 = __half2half2(__ldg(p.row_scale + n));
+  const bool has_scale = p.has_scale != 0;
+  if (has_scale) s2 = __half2half2(__ldg(p.row_scale + (has_scale ? n : 0)));
 #pragma unroll
   for (int c = 0; c < 8; ++c) {
     __half2 h[4];
@@ -563,12 +569,15 @@ void fill_fused_vq(FusedVq& v, const npb_vq_weight* w, int64_t K) {
   v.packed = w->packed;
   v.packed_bytes = w->packed_bytes;
   v.centroids = static_cast<const __half*>(w->centroids);
-  v.res_packed = w->res_packed;
-  v.res_bytes = w->res_packed_bytes;
-  v.res_centroids = static_cast<const __half*>(w->res_centroids);
-  v.row_scale = static_cast<const __half*>(w->row_scale);
+  v.has_res = w->res_packed != nullptr;
+  v.has_scale = w->row_scale != nullptr;
+  // Absent parts alias valid buffers and read entry 0 (never used in the result).
+  v.res_packed = v.has_res ? w->res_packed : w->packed;
+  v.res_bytes = v.has_res ? w->res_packed_bytes : 0;
+  v.res_centroids = v.has_res ? static_cast<const __half*>(w->res_centroids) : v.centroids;
+  v.row_scale = v.has_scale ? static_cast<const __half*>(w->row_scale) : v.centroids;
   v.bits = w->bits;
-  v.res_bits = w->res_bits;
+  v.res_bits = v.has_res ? w->res_bits : 0;
   v.num_centroids = w->num_centroids;
   v.groups_per_codebook = w->cols_per_codebook > 0 ? w->cols_per_codebook / 8 : 0;
   v.cb_rows = w->num_centroids *
@@ -595,6 +604,57 @@ __global__ void __launch_bounds__(128) vq_tile_probe_kernel(FusedVq v, int N, in
   decode_vq_row<T, BITS>(v, tn * 128 + row, N, K / 8, kb, smem_u32(tile), row);
   __syncthreads();
   for (int i = threadIdx.x; i < 128 * 8; i += 128) out[i] = reinterpret_cast<const uint4*>(tile)[i];
+}
+
+// Test hook 2: the decoder under the fused GEMM's geometry -- a 320-thread CTA whose warps 6-9
+// decode every K block of one 128-row tile into a ring of 32 KiB stages in dynamic shared
+// memory (W tile in the upper 16 KiB of a stage, as in the GEMM), while the other warps copy
+// each finished tile to global memory.  No TMA, no tcgen05, no mbarriers: plain barriers.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(320, 1) vq_ring_probe_kernel(FusedVq v, int N, int K, int tn, int stages,
+                                                               uint4* __restrict__ out) {
+  extern __shared__ uint8_t ring_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int kStage = 2 * kAStageBytes;   // A region (unused here) + W region
+  const int num_kb = K / BK;
+  const int warp = threadIdx.x >> 5;
+  for (int kb = 0; kb < num_kb; ++kb) {
+    const int s = kb % stages;
+    uint8_t* wtile = ring + (size_t)s * kStage + kAStageBytes;
+    if (warp >= 6) {
+      const int row = threadIdx.x - 6 * 32;
+      decode_vq_row<T, BITS>(v, tn * 128 + row, N, K / 8, kb, smem_u32(wtile), row);
+    }
+    __syncthreads();
+    if (warp < 6) {
+      for (int i = threadIdx.x; i < 128 * 8; i += 192)
+        out[(size_t)kb * 1024 + i] = reinterpret_cast<const uint4*>(wtile)[i];
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+int launch_ring_probe(const FusedVq& v, int vbits, int N, int K, int tn, void* out, cudaStream_t st) {
+  const int cap = max_dynamic_smem();
+  const int stages = SmemLayout<128, 1>::stages(cap);
+  const int smem = 1024 + stages * 2 * kAStageBytes;
+  uint4* o = static_cast<uint4*>(out);
+#define NPB_RING(BITS_)                                                                          \
+  do {                                                                                           \
+    auto kern = vq_ring_probe_kernel<T, BITS_>;                                                  \
+    NPB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    kern<<<1, 320, smem, st>>>(v, N, K, tn, stages, o);                                          \
+  } while (0)
+  switch (vbits) {
+    case 16: NPB_RING(16); break;
+    case 12: NPB_RING(12); break;
+    case 8: NPB_RING(8); break;
+    default: NPB_RING(0); break;
+  }
+#undef NPB_RING
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
 }
 
 template <typename T>
@@ -666,7 +726,7 @@ int vq_decode_tile_probe(const npb_vq_weight* w, int64_t N, int64_t K, int tile_
   if (int rc = validate_vq(w, N, K)) return rc;
   if (out == nullptr || w->vector_len != 8 || K % 64 != 0 || N <= 0) return NPB_ERR_UNSUPPORTED;
   if (dtype != NPB_BF16 && dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
-  if (tile_n < 0 || (int64_t)tile_n * 128 >= N || k_block < 0 || (int64_t)k_block * 64 >= K)
+  if (tile_n < 0 || (int64_t)tile_n * 128 >= N || k_block < -1 || (int64_t)k_block * 64 >= K)
     return NPB_ERR_INVALID_ARG;
   if (!aligned_to(out, 16) || !aligned_to(w->centroids, 16) ||
       (w->res_centroids && !aligned_to(w->res_centroids, 16)))
@@ -675,6 +735,9 @@ int vq_decode_tile_probe(const npb_vq_weight* w, int64_t N, int64_t K, int tile_
   fill_fused_vq(v, w, K);
   const int vbits = fused_vq_bits(w, v);
   if (vbits == 0 && v.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
+  if (k_block == -1)  // ring mode: all K blocks of the tile, out holds K/64 tile images
+    return dtype == NPB_BF16 ? launch_ring_probe<__nv_bfloat16>(v, vbits, (int)N, (int)K, tile_n, out, st)
+                             : launch_ring_probe<__half>(v, vbits, (int)N, (int)K, tile_n, out, st);
   return dtype == NPB_BF16
              ? launch_tile_probe<__nv_bfloat16>(v, vbits, (int)N, (int)K, tile_n, k_block, out, st)
              : launch_tile_probe<__half>(v, vbits, (int)N, (int)K, tile_n, k_block, out, st);

@@ -160,11 +160,9 @@ def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torc
     return _vq_call("npb_vq_gemm_fused", x, packed_indices, centroids, bits, out_features, bias, ext)
 
 
-# The VQ tile-decode GEMM is switched off: on a B200 it raised an illegal memory access that
-# reading has not explained (its decoder is verified bit-exact on its own through
-# ``vq_decode_tile``, and the same GEMM skeleton passes with the 4-bit decoder).  While off,
-# the mid-sized band runs the one-pass decode followed by the dense tensor-core GEMM.
-VQ_TILE_DECODE_GEMM = False
+# Whether the mid-sized band runs the tile-decode GEMM (``npb_vq_gemm_fused``); when False it
+# runs the one-pass decode followed by the dense tensor-core GEMM.
+VQ_TILE_DECODE_GEMM = True
 
 
 def vq_dequant_gemm(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
@@ -339,13 +337,15 @@ def vq_decode_tile(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: 
                        ext.get("residual_centroids"), ext.get("row_scale"))
     lib = _cabi.load_library()
     w = _cabi.vq_struct(packed_indices, centroids, bits, **ext)
-    raw = torch.empty(128 * 128, dtype=torch.uint8, device=packed_indices.device)
+    n_tiles = in_features // 64 if k_block == -1 else 1   # -1: every K block, through the ring
+    raw = torch.empty(n_tiles * 128 * 128, dtype=torch.uint8, device=packed_indices.device)
     with torch.cuda.device(packed_indices.device):
         rc = lib.npb_test_vq_decode_tile(w, out_features, in_features, tile_n, k_block,
                                          _cabi.dtype_code(dtype), raw.data_ptr(), _cabi.stream_ptr())
     _cabi.check(rc, "vq_decode_tile")
-    img = raw.view(128, 8, 16)
-    r = torch.arange(128, device=raw.device).view(128, 1)
-    c = torch.arange(8, device=raw.device).view(1, 8)
-    pos = (c ^ (r & 7)).unsqueeze(-1).expand(128, 8, 16)
-    return torch.gather(img, 1, pos).reshape(128, 128).view(dtype)
+    img = raw.view(n_tiles, 128, 8, 16)
+    r = torch.arange(128, device=raw.device).view(1, 128, 1)
+    c = torch.arange(8, device=raw.device).view(1, 1, 8)
+    pos = (c ^ (r & 7)).unsqueeze(-1).expand(n_tiles, 128, 8, 16)
+    out = torch.gather(img, 2, pos).reshape(n_tiles, 128, 128).view(dtype)
+    return out if k_block == -1 else out[0]

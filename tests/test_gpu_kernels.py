@@ -191,6 +191,27 @@ def test_vq_tile_decoder_bit_exact(case, dtype):
             want = ref_pad[tn * 128:(tn + 1) * 128, kb * 64:(kb + 1) * 64]
             torch.testing.assert_close(tile.cpu(), want, rtol=0, atol=0)
 
+
+@pytest.mark.parametrize("case", TILE_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_vq_ring_decoder_bit_exact(case, dtype):
+    """The same decoder under the fused GEMM's thread / shared-memory geometry (320-thread CTA,
+    decode warps 6-9, ring of 32 KiB stages in dynamic shared memory), every K block of a tile."""
+    N, K, NC, bits, res, scale, cpc = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K, residual_centroids=res,
+                          row_scale=scale, cols_per_codebook=cpc)
+    ref = _decode_ref(layer, dtype)
+    ref_pad = torch.zeros((N + 127) // 128 * 128, K, dtype=dtype)
+    ref_pad[:N] = ref
+    for tn in {0, (N - 1) // 128}:
+        ring = kernels.vq_decode_tile(layer.packed.to(DEV), layer.centroids.to(DEV), bits, N, K, tn, -1,
+                                      dtype, **_vq_ext_gpu(layer))
+        want = ref_pad[tn * 128:(tn + 1) * 128].reshape(128, K // 64, 64).permute(1, 0, 2)
+        torch.testing.assert_close(ring.cpu(), want, rtol=0, atol=0)
+    from neuropress_b200 import _cabi
+    assert _cabi.gemm_device_status() == 0
+
+
 FUSED_CASES = [
     (256, 512, 4096, 16, 0, False, 0),
     (200, 1024, 4096, 12, 0, False, 0),
@@ -201,7 +222,6 @@ FUSED_CASES = [
 ]
 
 
-@pytest.mark.skip(reason="npb_vq_gemm_fused is switched off: see kernels.VQ_TILE_DECODE_GEMM")
 @pytest.mark.parametrize("case", FUSED_CASES)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows", [9, 17, 128, 130, 300, 384])
