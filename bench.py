@@ -72,6 +72,7 @@ class ClockSampler:
         self.index = index
         self.samples: list[list[str]] = []
         self._stop = threading.Event()
+        self._ready = threading.Event()  # set once the first sample is in (or sampling failed)
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run_nvml(self) -> bool:
@@ -93,7 +94,7 @@ class ClockSampler:
         except Exception:
             return False
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        while not self._stop.is_set():
+        while True:
             try:
                 sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
                 mask = get_reasons(h)
@@ -101,13 +102,16 @@ class ClockSampler:
                                     ["Active" if mask & bits[n] else "Not Active" for n in names])
             except Exception:
                 pass
-            self._stop.wait(0.005)
+            self._ready.set()
+            if self._stop.wait(0.002):
+                break
         return True
 
     def _run(self) -> None:
         if self._run_nvml():
             return
         while not self._stop.is_set():
+            self._ready.set()
             try:
                 out = subprocess.run(
                     ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
@@ -120,6 +124,7 @@ class ClockSampler:
 
     def __enter__(self):
         self._thread.start()
+        self._ready.wait(timeout=10)  # NVML start-up must not eat a short timed region
         return self
 
     def __exit__(self, *exc):

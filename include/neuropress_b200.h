@@ -128,7 +128,8 @@ int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_
                       int64_t N, int64_t K, const float* bias, void* y, npb_stream_t stream);
 
 /* Same for group-affine weights (no reference counterpart beyond q_linear, which re-reads
- * the weight per row: neuropress/kernels/q4_linear.cu:80-131). nbits 4, K % 64 == 0. */
+ * the weight per row: neuropress/kernels/q4_linear.cu:80-131). nbits 4, K % 64 == 0,
+ * group_size % 32 == 0 (NPB_ERR_UNSUPPORTED otherwise: decode, then npb_gemm). */
 int npb_q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
                      int64_t K, const float* bias, void* y, npb_stream_t stream);
 

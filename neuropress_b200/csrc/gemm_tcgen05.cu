@@ -43,6 +43,7 @@ constexpr int BK = 64;            // 64 x 16-bit = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kAStageBytes = BM * BK * 2;                 // 16 KiB per 128-row A sub-tile
 constexpr uint64_t kWaitTimeoutNs = 2000000000ull;        // 2 s
+constexpr int kSmemCapAssumed = 232448;                   // opt-in dynamic shared memory per CTA on sm_100
 
 enum BMode { B_TMA = 0, B_VQ = 1, B_Q4 = 2 };
 
@@ -65,8 +66,9 @@ struct FusedVq {
 struct FusedQ4 {
   const uint8_t* codes;
   const __half* scale;
-  const __half* zp;
-  int group_size;
+  const __half* zp;   // never null: aliases `scale` when the weight is symmetric (has_zp == 0)
+  int group_size;     // a multiple of 32 on the fused path
+  int has_zp;
 };
 
 struct GemmParams {
@@ -87,6 +89,14 @@ struct SmemLayout {
     return s > 8 ? 8 : s;
   }
 };
+
+// Ring depth and decode warps of the 4-bit fused mode: at most six stages so that four warps
+// per stage (24 decode warps + 6 role warps = 960 threads) fit one CTA.
+constexpr int kQ4DecodeWarps = 24;
+template <int BN, int MT>
+constexpr int q4_stages() {
+  return SmemLayout<BN, MT>::stages(kSmemCapAssumed) > 6 ? 6 : SmemLayout<BN, MT>::stages(kSmemCapAssumed);
+}
 
 // ---- B tile decoders (fused modes) ---------------------------------------------------------
 // One decode thread owns one W row of the tile (BN == 128 == decode threads) and writes its
@@ -194,38 +204,118 @@ __device__ __forceinline__ void decode_vq_row(const FusedVq& p, int n, int N, in
   }
 }
 
-template <typename T>
-__device__ __forceinline__ void decode_q4_row(const FusedQ4& p, int n, int N, int K, int kb,
-                                              uint32_t b_stage, int row) {
-  const uint32_t row_addr = b_stage + row * 128;
-  const int sw = row & 7;
-  if (n >= N) {
-    const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) st_shared_v4(row_addr + ((c ^ sw) << 4), z);
-    return;
-  }
+// 4-bit group-affine decoder.  Every ring stage has its own decode warp(s): with S stages and
+// R warps per stage, warp w serves stage w % S only, i.e. the CTA's (tile, K block) items
+// w % S, w % S + S, ... -- consecutive phases of that stage's barriers, which is what makes a
+// one-bit parity wait unambiguous -- and decodes rows [128/R * (w / S), +128/R) of the tile.
+// The per-stage handshake (empty wait, proxy fence, arrive) is thus paid once per 8192 / R
+// elements per warp, and all S stages are decoded concurrently.  A lane owns rows lane + 32 r:
+// 32 code bytes per row and K block (one fully used 32-byte sector).  The raw bytes of a
+// warp's next item are fetched (q4_fetch) before the current one is converted (q4_emit),
+// which keeps the global-load latency off the critical path.
+template <int RPL>  // rows per lane
+struct Q4Item {
+  uint4 c[RPL][2];     // [row][half of the K block]
+  __half s[RPL][2], z[RPL][2];  // raw: converting here would wait for the loads at fetch time
+};
+
+// n0: first W row of this warp's share of the tile; the lane's rows are n0 + lane + 32 r.
+template <int RPL>
+__device__ __forceinline__ void q4_fetch(Q4Item<RPL>& it, const FusedQ4& p, int n0, int N, int K, int kb,
+                                         int lane) {
   const int groups = K / p.group_size;
-  const uint8_t* cp = p.codes + (size_t)n * (K / 2) + kb * 32;
-  const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(cp));
-  const uint4 c1 = __ldg(reinterpret_cast<const uint4*>(cp) + 1);
-  const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const int g0 = (kb * 64) / p.group_size, g1 = (kb * 64 + 32) / p.group_size;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const int g = (kb * 64 + c * 8) / p.group_size;
-    const float s = __half2float(__ldg(p.scale + (size_t)n * groups + g));
-    const float z = p.zp ? __half2float(__ldg(p.zp + (size_t)n * groups + g)) : 8.f;
-    T v[8];
+  for (int r = 0; r < RPL; ++r) {
+    // Rows past N read row N-1 (always mapped); q4_emit gives them scale 0 and their columns
+    // are never stored.
+    const int n = n0 + lane + 32 * r;
+    const int nn = n < N ? n : N - 1;
+    const uint4* cp = reinterpret_cast<const uint4*>(p.codes + (size_t)nn * (K / 2) + kb * 32);
+    it.c[r][0] = __ldg(cp);
+    it.c[r][1] = __ldg(cp + 1);
+    const size_t gb = (size_t)nn * groups;
+    it.s[r][0] = __ldg(p.scale + gb + g0);
+    it.s[r][1] = __ldg(p.scale + gb + g1);
+    it.z[r][0] = __ldg(p.zp + gb + g0);
+    it.z[r][1] = __ldg(p.zp + gb + g1);
+  }
+}
+
+// Packed fp32 (two lanes per instruction, sm_100), round-to-nearest, one rounding each.
+__device__ __forceinline__ float2 fsub2(const float2 a, const float2 b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return reinterpret_cast<const float2&>(d);
+}
+__device__ __forceinline__ float2 fmul2(const float2 a, const float2 b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(d)
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return reinterpret_cast<const float2&>(d);
+}
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
+  const __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// (q - z) * s in fp32 with one rounding per operation, exactly as the one-pass decode does,
+// two elements per instruction (packed fp32).  0x4B000000 | q is the float 2^23 + q, so
+// subtracting 2^23 yields q without an int-to-float conversion; for a symmetric weight
+// (z = 8) both subtractions fold into one exact one.
+template <typename T, bool ASYM>
+__device__ __forceinline__ void q4_emit_half(const uint4& codes, __half sh, __half zh, bool valid,
+                                             uint32_t row_addr, int sw, int half) {
+  const float s = valid ? __half2float(sh) : 0.f;
+  const float z = __half2float(zh);
+  const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+  const float2 s2 = make_float2(s, s);
+  const float2 m2 = ASYM ? make_float2(8388608.f, 8388608.f) : make_float2(8388616.f, 8388616.f);
+  const float2 z2 = make_float2(z, z);
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      v[e] = from_f32<T>(__fmul_rn(__fsub_rn((float)((words[c] >> (4 * e)) & 0xfu), z), s));
-    st_shared_v4(row_addr + ((c ^ sw) << 4), *reinterpret_cast<const uint4*>(v));
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t lo = words[j] & 0x0f0f0f0fu;         // elements 0, 2, 4, 6 (one per byte)
+    const uint32_t hi = (words[j] >> 4) & 0x0f0f0f0fu;  // elements 1, 3, 5, 7
+    uint32_t o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // byte e of lo / hi into the low byte of 0x4B000000
+      float2 q = make_float2(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7650 + e)),
+                             __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7650 + e)));
+      q = fsub2(q, m2);
+      if (ASYM) q = fsub2(q, z2);
+      q = fmul2(q, s2);
+      o[e] = pack2(q.x, q.y, T());
+    }
+    st_shared_v4(row_addr + (((half * 4 + j) ^ sw) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+  }
+}
+
+// row0: tile row of the warp's first row (n0 = tile's first W row + row0).
+template <typename T, bool ASYM, int RPL>
+__device__ __forceinline__ void q4_emit(const Q4Item<RPL>& it, int n0, int N, uint32_t b_stage, int row0,
+                                        int lane) {
+#pragma unroll
+  for (int r = 0; r < RPL; ++r) {
+    const int row = row0 + lane + 32 * r;
+    const bool valid = n0 + lane + 32 * r < N;
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      q4_emit_half<T, ASYM>(it.c[r][h], it.s[r][h], it.z[r][h], valid, b_stage + row * 128, row & 7, h);
   }
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
 template <typename T, int BN, int MT, int BMODE, int BITS>
-__global__ void __launch_bounds__(BMODE == B_TMA ? 192 : 320, 1)
+__global__ void __launch_bounds__(BMODE == B_TMA ? 192 : BMODE == B_VQ ? 320 : 192 + 32 * kQ4DecodeWarps, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p, const int stages) {
   constexpr int ACC_COLS = MT * BN;                       // fp32 columns per accumulator buffer
@@ -234,7 +324,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                           : (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256) ? 256 : 512;
   constexpr int BUF_STRIDE = (NBUF == 2) ? TMEM_COLS / 2 : 0;
   constexpr int kStageBytes = SmemLayout<BN, MT>::kStageBytes;
-  constexpr int kNumDecodeWarps = (BMODE == B_TMA) ? 0 : 4;
+  // Q4: S stages x R warps per stage (see the decoder notes); VQ: four warps share every stage.
+  constexpr int kQ4Stages = q4_stages<BN, MT>();
+  constexpr int kQ4WarpsPerStage = 4;
+  constexpr int kNumDecodeWarps = (BMODE == B_TMA) ? 0 : (BMODE == B_VQ) ? 4 : kQ4Stages * kQ4WarpsPerStage;
+  constexpr int kFullArrivals = (BMODE == B_TMA) ? 0 : (BMODE == B_VQ) ? 4 : kQ4WarpsPerStage;
+  static_assert(BMODE != B_Q4 || kNumDecodeWarps <= kQ4DecodeWarps, "decode warps of the Q4 launch");
   constexpr uint32_t kIdesc = umma_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
   static_assert(BMODE == B_TMA || BN == 128, "fused decode maps one decode thread to one W row");
@@ -258,7 +353,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full_bar[s], 1 + kNumDecodeWarps);
+      mbar_init(&full_bar[s], 1 + kFullArrivals);
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -287,7 +382,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int tm = t % p.tiles_m, tn = t / p.tiles_m;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs)) {
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs,
+                                 BMODE == B_TMA ? 0u : 128u)) {
             atomicExch(&g_gemm_status, 1);
             ok = false;
             break;
@@ -358,7 +454,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
       // All lanes wait (each needs the acquire), then agree on the outcome so that the
       // warp-collective tcgen05.ld below is never reached by part of a warp.
-      const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, kWaitTimeoutNs);
+      const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, kWaitTimeoutNs,
+                                         BMODE == B_TMA ? 0u : 512u);
       if (!__all_sync(0xffffffffu, got)) {
         atomicExch(&g_gemm_status, 3);
         break;
@@ -411,7 +508,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else {
     // ================= B decoders (fused modes only) =================
-    if constexpr (BMODE != B_TMA) {
+    if constexpr (BMODE == B_VQ) {
       const int row = threadIdx.x - 6 * 32;  // 0..127
       const int G = p.K / 8;
       int s = 0;
@@ -421,19 +518,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int tn = t / p.tiles_m;
         const int n = tn * BN + row;
         for (int kb = 0; kb < num_kb; ++kb) {
-          const bool got = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs);
+          const bool got = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs, 128u);
           if (!__all_sync(0xffffffffu, got)) {
             atomicExch(&g_gemm_status, 4);
             ok = false;
             break;
           }
           const uint32_t b_stage = smem_u32(stage_base + (size_t)s * kStageBytes + MT * kAStageBytes);
-          if constexpr (BMODE == B_VQ) decode_vq_row<T, BITS>(p.vq, n, p.N, G, kb, b_stage, row);
-          else decode_q4_row<T>(p.q4, n, p.N, p.K, kb, b_stage, row);
+          decode_vq_row<T, BITS>(p.vq, n, p.N, G, kb, b_stage, row);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&full_bar[s]);
           if (++s == stages) { s = 0; ph ^= 1; }
+        }
+      }
+    } else if constexpr (BMODE == B_Q4) {
+      constexpr int S = kQ4Stages, R = kQ4WarpsPerStage, RPL = 4 / R;
+      const int dw = warp - 6;  // warps past S * R have no stage
+      if (dw < S * R) {
+        const int slot = dw % S, row0 = (dw / S) * (128 / R);
+        const int my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int total = my_tiles * num_kb;  // (tile, K block) items of this CTA, in ring order
+        const bool asym = p.q4.has_zp != 0;
+        const uint32_t b_stage = smem_u32(stage_base + (size_t)slot * kStageBytes + MT * kAStageBytes);
+        auto warp_n0 = [&](int i) {
+          return ((blockIdx.x + (i / num_kb) * gridDim.x) / p.tiles_m) * BN + row0;
+        };
+        // Decode item i from `cur` while this warp's next item, i + S, is fetched into `nxt`.
+        auto step = [&](Q4Item<RPL>& cur, Q4Item<RPL>& nxt, int i) -> bool {
+          if (i + S < total) q4_fetch<RPL>(nxt, p.q4, warp_n0(i + S), p.N, p.K, (i + S) % num_kb, lane);
+          const uint32_t ph = (uint32_t)(i / S) & 1u;
+          const bool got = mbar_wait_bounded(&empty_bar[slot], ph ^ 1, abort_flag, kWaitTimeoutNs, 128u);
+          if (!__all_sync(0xffffffffu, got)) {
+            atomicExch(&g_gemm_status, 4);
+            return false;
+          }
+          if (asym) q4_emit<T, true, RPL>(cur, warp_n0(i), p.N, b_stage, row0, lane);
+          else q4_emit<T, false, RPL>(cur, warp_n0(i), p.N, b_stage, row0, lane);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[slot]);
+          return true;
+        };
+        Q4Item<RPL> a, b;
+        if (slot < total) q4_fetch<RPL>(a, p.q4, warp_n0(slot), p.N, p.K, slot % num_kb, lane);
+        for (int i = slot; i < total; i += 2 * S) {
+          if (!step(a, b, i)) break;
+          if (i + S < total && !step(b, a, i + S)) break;
         }
       }
     }
@@ -499,8 +630,13 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
   constexpr bool bf16 = std::is_same<T, __nv_bfloat16>::value;
   auto kern = gemm_kernel<T, BN, MT, BMODE, BITS>;
   const int cap = max_dynamic_smem();
-  const int stages = SmemLayout<BN, MT>::stages(cap);
+  int stages = SmemLayout<BN, MT>::stages(cap);
   if (stages < 2) return NPB_ERR_UNSUPPORTED;
+  // The 4-bit decoder binds its warps to ring stages at compile time.
+  if (BMODE == B_Q4) {
+    if (stages < q4_stages<BN, MT>()) return NPB_ERR_UNSUPPORTED;
+    stages = q4_stages<BN, MT>();
+  }
   const int smem = SmemLayout<BN, MT>::kBarrierBytes + 1024 + stages * SmemLayout<BN, MT>::kStageBytes;
   static int configured[64] = {0};
   int dev = 0;
@@ -520,7 +656,7 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  constexpr int threads = BMODE == B_TMA ? 192 : 320;
+  constexpr int threads = BMODE == B_TMA ? 192 : BMODE == B_VQ ? 320 : 192 + 32 * kQ4DecodeWarps;
   kern<<<grid, threads, smem, st>>>(ta, tb, p, stages);
   NPB_LAUNCH_CHECK();
   return NPB_OK;
@@ -748,7 +884,7 @@ int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, i
   if (int rc = validate_q(w, N, K)) return rc;
   if (int rc = check_gemm_common(x, y, M, N, K, x_dtype)) return rc;
   if (M == 0 || N == 0) return NPB_OK;
-  if (w->nbits != 4 || K % 64 != 0) return NPB_ERR_UNSUPPORTED;
+  if (w->nbits != 4 || K % 64 != 0 || w->group_size % 32 != 0) return NPB_ERR_UNSUPPORTED;
   if (!aligned_to(w->codes, 16)) return NPB_ERR_ALIGNMENT;
   GemmParams p{};
   p.bias = bias;
@@ -756,7 +892,8 @@ int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, i
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.q4.codes = w->codes;
   p.q4.scale = static_cast<const __half*>(w->scale);
-  p.q4.zp = static_cast<const __half*>(w->zero_point);
+  p.q4.has_zp = w->zero_point != nullptr;
+  p.q4.zp = p.q4.has_zp ? static_cast<const __half*>(w->zero_point) : p.q4.scale;
   p.q4.group_size = w->group_size;
   return x_dtype == NPB_BF16 ? gemm_fused_mt<__nv_bfloat16, B_Q4, 0>(x, p, st)
                              : gemm_fused_mt<__half, B_Q4, 0>(x, p, st);

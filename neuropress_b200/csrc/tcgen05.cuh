@@ -48,12 +48,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Wait for `parity` of `bar`, giving up after `timeout_ns` or as soon as another thread of
 // the CTA raised *abort_flag.  Returns false on give-up (and raises the flag itself).
+// `sleep_ns` > 0 backs off between polls: polling warps otherwise compete with the warps that
+// do the work for issue slots and for the shared-memory pipe the barrier lives in.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* abort_flag,
-                                                  uint64_t timeout_ns) {
+                                                  uint64_t timeout_ns, uint32_t sleep_ns = 0) {
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((spin & 255u) == 255u) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();

@@ -7,7 +7,10 @@
 // (neuropress/kernels/vq_dequant.cu:50-83): pure indexing plus one conversion, so the
 // result is bit-exact.  One thread decodes one vector per step; lanes take consecutive
 // vectors so that index loads (2 B/lane) and stores (VL*sizeof(T) per lane) are contiguous
-// across the warp.  HBM traffic = packed bytes + N*K*sizeof(T); the kernel is write-bound.
+// across the warp.  HBM traffic = packed bytes + N*K*sizeof(T).  With a codebook that stays in
+// L1 the kernel is write-bound; with a 1 MiB codebook every gather misses L1 and pulls a
+// 32-byte sector from L2, and the sum of gather sectors, index reads and output writes runs
+// at the L2's throughput (measured: ~8 TB/s), which then bounds it.
 #include "common.cuh"
 
 namespace npb {
@@ -25,6 +28,9 @@ struct VqDev {
   const __half* res_centroids;
   const __half* row_scale;
   int bits, res_bits, num_centroids, groups_per_codebook;  // groups_per_codebook 0: single
+  // Whether the optional parts exist.  Their pointers are never null (an absent part aliases
+  // the main stream / codebook), so a load hoisted above the test still reads mapped memory.
+  int has_res, has_scale;
 };
 
 template <int VL>
@@ -63,7 +69,8 @@ vq_decode_kernel(VqDev a, T* __restrict__ out, uint32_t n_vectors, uint32_t G) {
   using HV = typename HVec<VL>::type;
   const uint32_t base = blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
   uint32_t idx[kUnroll], ridx[kUnroll];
-  const bool has_res = a.res_packed != nullptr;
+  const bool has_res = a.has_res != 0;
+  const bool has_scale = a.has_scale != 0;
 #pragma unroll
   for (int u = 0; u < kUnroll; ++u) {
     const uint32_t v = base + u * kThreads;
@@ -79,7 +86,7 @@ vq_decode_kernel(VqDev a, T* __restrict__ out, uint32_t n_vectors, uint32_t G) {
     if (v >= n_vectors) continue;
     uint32_t row_off = idx[u];
     uint32_t n = 0;
-    if (a.groups_per_codebook > 0 || a.row_scale != nullptr) {
+    if (a.groups_per_codebook > 0 || has_scale) {
       n = v / G;
       const uint32_t g = v - n * G;
       if (a.groups_per_codebook > 0)
@@ -94,8 +101,8 @@ vq_decode_kernel(VqDev a, T* __restrict__ out, uint32_t n_vectors, uint32_t G) {
 #pragma unroll
       for (int i = 0; i < VL / 2; ++i) h[i] = __hadd2_rn(h[i], r.h[i]);
     }
-    if (a.row_scale != nullptr) {
-      const __half2 s = __half2half2(__ldg(a.row_scale + n));
+    if (has_scale) {
+      const __half2 s = __half2half2(__ldg(a.row_scale + (has_scale ? n : 0u)));
 #pragma unroll
       for (int i = 0; i < VL / 2; ++i) h[i] = __hmul2_rn(h[i], s);
     }
@@ -109,7 +116,7 @@ int launch_decode(const VqDev& a, T* out, uint32_t n_vectors, uint32_t G, cudaSt
   const uint32_t blocks = (n_vectors + per_block - 1) / per_block;
   const bool a16 = a.bits == 16 && aligned_to(a.packed, 2);
   const bool a8 = a.bits == 8;
-  const bool r8 = a.res_packed == nullptr || a.res_bits == 8;
+  const bool r8 = !a.has_res || a.res_bits == 8;
   if (a16 && r8)
     vq_decode_kernel<T, VL, 16, 8><<<blocks, kThreads, 0, st>>>(a, out, n_vectors, G);
   else if (a8 && r8)
@@ -142,12 +149,14 @@ int vq_decode(const npb_vq_weight* w, int64_t N, int64_t K, void* out, int out_d
   a.packed = w->packed;
   a.packed_bytes = w->packed_bytes;
   a.centroids = static_cast<const __half*>(w->centroids);
-  a.res_packed = w->res_packed;
-  a.res_bytes = w->res_packed_bytes;
-  a.res_centroids = static_cast<const __half*>(w->res_centroids);
-  a.row_scale = static_cast<const __half*>(w->row_scale);
+  a.has_res = w->res_packed != nullptr;
+  a.has_scale = w->row_scale != nullptr;
+  a.res_packed = a.has_res ? w->res_packed : w->packed;
+  a.res_bytes = a.has_res ? w->res_packed_bytes : 0;
+  a.res_centroids = a.has_res ? static_cast<const __half*>(w->res_centroids) : a.centroids;
+  a.row_scale = a.has_scale ? static_cast<const __half*>(w->row_scale) : a.centroids;
   a.bits = w->bits;
-  a.res_bits = w->res_bits;
+  a.res_bits = a.has_res ? w->res_bits : 0;
   a.num_centroids = w->num_centroids;
   a.groups_per_codebook = w->cols_per_codebook > 0 ? w->cols_per_codebook / w->vector_len : 0;
   switch (out_dtype) {

@@ -161,8 +161,11 @@ def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torc
 
 
 # Whether the mid-sized band runs the tile-decode GEMM (``npb_vq_gemm_fused``); when False it
-# runs the one-pass decode followed by the dense tensor-core GEMM.
-VQ_TILE_DECODE_GEMM = True
+# runs the one-pass decode followed by the dense tensor-core GEMM.  Off: on a B200 the
+# decode + GEMM pair was faster on every shape measured (e.g. 14336 x 4096 with a 65536-entry
+# codebook, 128 rows: 82 us against 139 us) -- the centroid gathers bound both, and the
+# whole-GPU decode kernel keeps far more of them in flight than four decode warps per CTA.
+VQ_TILE_DECODE_GEMM = False
 
 
 def vq_dequant_gemm(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
@@ -295,6 +298,10 @@ def q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point=None, bias=None
 # Row count up to which q_linear re-decodes the weight inside the GEMM; above it the weight is
 # decoded once and the dense GEMM runs (the tile-dequant GEMM repeats the decode per 384 rows).
 Q_FUSED_MAX_ROWS = 384
+# The tile-dequant GEMM runs one CTA per 128 output features, so it only pays when those CTAs
+# cover most of the GPU (measured on 148 SMs: 14336 features, 128 rows: 51 us against 63 us
+# for decode + GEMM; 4096 features: 50 us against 32 us).
+Q_FUSED_MIN_TILES = 96
 
 
 def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: int,
@@ -310,7 +317,8 @@ def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: 
         return q_gemv(x, w_pack, scale, nbits, group_size, zero_point, bias)
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("q_linear: more than 8 rows need fp16 or bf16 activations.")
-    if m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0:
+    if (m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0 and group_size % 32 == 0
+            and (w_pack.shape[0] + 127) // 128 >= Q_FUSED_MIN_TILES):
         return q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point, bias)
     w = q_dequant(w_pack, scale, nbits, group_size, zero_point, x.dtype)
     *leading, _ = x.shape

@@ -252,3 +252,26 @@ def test_q_gemm_fused_matches_oracle(asym, gs, dtype, rows, shape):
     assert _cabi.gemm_device_status() == 0
     ref = oracle.q_forward_f64(x, layer.codes, layer.scale, 4, gs, layer.zero_point, layer.bias)
     assert_output_close(y, ref, dtype, tol=2e-3)
+
+
+@pytest.mark.parametrize("asym,gs,rows", [(True, 64, 130), (False, 32, 384)])
+def test_q_gemm_fused_full_size_layer(asym, gs, rows):
+    """14336 x 4096: 112 CTAs, 64 K blocks each, so every ring stage wraps many times."""
+    N, K = 14336, 4096
+    layer = make_q_layer(N, K, group_size=gs, asym=asym, seed=gs)
+    x = make_activations(rows, K, torch.bfloat16, seed=rows)
+    y = kernels.q_gemm_fused(x.to(DEV), layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                             None if layer.zero_point is None else layer.zero_point.to(DEV))
+    from neuropress_b200 import _cabi
+    assert _cabi.gemm_device_status() == 0
+    # same weights as the one-pass decode (bit-exact by construction), so compare with the
+    # dense path on the GPU exactly and with the oracle on a slice of the output
+    w = kernels.q_dequant(layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                          None if layer.zero_point is None else layer.zero_point.to(DEV), torch.bfloat16)
+    y_dense = kernels.gemm(x.to(DEV), w)
+    assert_output_close(y, y_dense.double().cpu(), torch.bfloat16, tol=2e-3)
+    sl = slice(5000, 5256)
+    ref = oracle.q_forward_f64(x, layer.codes[sl], layer.scale.view(N, -1)[sl].reshape(-1), 4, gs,
+                               None if layer.zero_point is None else layer.zero_point.view(N, -1)[sl].reshape(-1),
+                               None)
+    assert_output_close(y[:, sl], ref, torch.bfloat16, tol=2e-3)
