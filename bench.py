@@ -285,13 +285,52 @@ def run_ours(args) -> dict:
     step(True)
     barrier()
 
-    # ---- timed region: K steps, device-resident inputs, per-launch events
-    kernels.set_launch_hook(count_hook)
+    # ---- CUDA graphs of the step.  A step rotates through half of the weight copies, so two
+    # graphs (one per half) replayed alternately reproduce the eager sequence exactly; each
+    # holds the six module forwards of one step (and, for N > 1, their six push all-gathers).
+    graphs = None
+    if not args.eager and N_COPIES == 2 * len(ROWS) and (world == 1 or gather_kind.startswith("peer-store")):
+        graphs, keep = [], []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for phase in range(2):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for j, m in enumerate(ROWS):
+                        keep.append(layers[phase * len(ROWS) + j](xs[m]))
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        for _ in range(3):
+            for g in graphs:
+                g.replay()
+        barrier()
+
+    def timed_graph(steps: int) -> float:
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for s_ in range(steps):
+            graphs[s_ & 1].replay()
+        t1.record()
+        barrier()
+        ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- timed regions: K steps with device-resident inputs (graph replay when available),
+    # K eager steps with one CUDA-event pair per launch (kernel durations for the rooflines),
+    # K end-to-end steps from / to pinned host memory.
     with ClockSampler(local_rank) as clocks:
-        total_ms = timed(False, args.steps)
+        graph_ms = timed_graph(args.steps) if graphs else None
+        counter["i"] = 0
+        kernels.set_launch_hook(count_hook)
+        eager_ms = timed(False, args.steps)
         launches = counter["launches"]
         kernels.set_launch_hook(None)
         e2e_ms = timed(True, args.steps)
+    total_ms = graph_ms if graph_ms is not None else eager_ms
     kmean = timer.mean_ms()
 
     peaks, peak_src = load_peaks()
@@ -353,7 +392,10 @@ def run_ours(args) -> dict:
                                + "/".join(map(str, ROWS)),
                    "tokens_per_step": tokens_per_step,
                    "l2": f"cold: {N_COPIES} weight copies ({N_COPIES * packed_bytes / 1e6:.0f} MB) rotated per forward",
-                   "parallelism": "single GPU" if world == 1 else f"out-feature shards x{world} + {gather_kind}"},
+                   "parallelism": "single GPU" if world == 1 else f"out-feature shards x{world} + {gather_kind}",
+                   "launch": ("CUDA-graph replay of the module forwards (two graphs, one per half of the "
+                              "weight copies)") if graphs else "eager module forwards"},
+        "eager_ms_per_step": round(eager_ms / args.steps, 4),
         "e2e": {"value": round(tokens_per_step * args.steps / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": tokens_per_step * K_IN * 2,
                 "d2h_bytes_per_step": tokens_per_step * N_OUT * 2,
@@ -510,6 +552,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true",
+                    help="time eager launches instead of CUDA-graph replay")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="N > 1: all-gather with NCCL instead of the peer-store push kernel")
     args = ap.parse_args()

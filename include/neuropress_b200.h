@@ -169,13 +169,42 @@ int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dt
  * flags every peer and waits (at most 2 s) for all peers' flags, so when the kernel ends the
  * local buffer holds the full [M, N].  peer_out / peer_flags are DEVICE arrays of `world`
  * pointers (symmetric-memory buffer addresses of ranks 0..world-1); each rank's flag buffer
- * holds world + 2 zero-initialised uint32 words (per-peer epochs, a counter, a status word
- * that becomes 1 if a wait gave up).  epoch must increase by one per call on all ranks.
- * n_local * elem_bytes must be a multiple of 16.  One rank per GPU.
+ * holds world + 3 zero-initialised uint32 words (per-peer epochs, a counter, a status word
+ * that becomes 1 if a wait gave up, a call counter).  epoch must increase by one per call on
+ * all ranks; epoch 0 means "use the call counter kept in the flag words", which keeps the
+ * arguments constant from call to call (CUDA-graph replay).  Do not mix the two on one flag
+ * buffer.  n_local * elem_bytes must be a multiple of 16.  One rank per GPU.
  */
 int npb_allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem_bytes,
                        const void* peer_out, const void* peer_flags, int rank, int world,
                        uint32_t epoch, npb_stream_t stream);
+
+/*
+ * Fused compute + all-gather: the producing kernel stores this rank's [M, N_local] result
+ * straight into columns [col0, col0 + N_local) of every rank's [M, ld] buffer (peer stores
+ * from the GEMM epilogue / the GEMV's final store) and ends with the handshake of
+ * npb_allgather_push, so no separate gather pass runs.  Same flag words, epochs and rules as
+ * npb_allgather_push; all buffers 16-byte aligned, ld and col0 in elements of the activation
+ * dtype.  Every rank must make the call (M > 0).  npb_vq_gemv_allgather takes M <= 8 rows.
+ */
+typedef struct npb_gather_sink {
+  const void* peer_out;    /* device array [world] of buffer base pointers */
+  const void* peer_flags;  /* device array [world] of flag-word pointers */
+  int64_t ld;
+  int64_t col0;
+  int32_t rank;
+  int32_t world;
+  uint32_t epoch;          /* 0: epochs kept in the flag words (CUDA-graph friendly) */
+  uint32_t reserved;
+} npb_gather_sink;
+
+int npb_gemm_allgather(const void* x, const void* w, const float* bias, int64_t M,
+                       int64_t N_local, int64_t K, int dtype, const npb_gather_sink* sink,
+                       npb_stream_t stream);
+int npb_vq_gemv_allgather(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
+                          int64_t N_local, int64_t K, const float* bias,
+                          const npb_gather_sink* sink, npb_stream_t stream);
+
 
 /* Test hook, no reference counterpart: runs the tile decoder of npb_vq_gemm_fused on one
  * 128-row x 64-column W tile (rows [128*tile_n, +128), columns [64*k_block, +64)) and writes

@@ -38,6 +38,8 @@ EXPORTED_SYMBOLS = (
     "npb_q_gemm_fused",
     "npb_vq_linear_static_scratch",
     "npb_allgather_push",
+    "npb_gemm_allgather",
+    "npb_vq_gemv_allgather",
     "npb_test_vq_decode_tile",
     "npb_gemm_device_status",
 )
@@ -72,6 +74,21 @@ class QWeightStruct(Structure):
         ("zero_point", c_void_p),
         ("nbits", c_int32),
         ("group_size", c_int32),
+    ]
+
+
+class GatherSinkStruct(Structure):
+    """Mirror of ``npb_gather_sink``."""
+
+    _fields_ = [
+        ("peer_out", c_void_p),
+        ("peer_flags", c_void_p),
+        ("ld", c_int64),
+        ("col0", c_int64),
+        ("rank", c_int32),
+        ("world", c_int32),
+        ("epoch", ctypes.c_uint32),
+        ("reserved", ctypes.c_uint32),
     ]
 
 
@@ -115,6 +132,11 @@ def load_library() -> ctypes.CDLL:
                                             c_void_p]
     lib.npb_allgather_push.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int,
                                        c_int, ctypes.c_uint32, c_void_p]
+    sink_p = POINTER(GatherSinkStruct)
+    lib.npb_gemm_allgather.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                       sink_p, c_void_p]
+    lib.npb_vq_gemv_allgather.argtypes = [vq_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p,
+                                          sink_p, c_void_p]
     lib.npb_gemm_device_status.argtypes = [POINTER(c_int)]
     for name in EXPORTED_SYMBOLS[3:]:
         getattr(lib, name).restype = c_int

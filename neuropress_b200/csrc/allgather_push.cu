@@ -12,6 +12,7 @@
 // Ranks must run on different GPUs: two ranks waiting on each other on one GPU may never be
 // resident together.
 #include "common.cuh"
+#include "gather_sink.cuh"
 
 namespace npb {
 namespace {
@@ -25,53 +26,50 @@ struct PushArgs {
   uint32_t epoch;
 };
 
-// Flag words of one rank: [0, world) = "slice of rank q has landed here" epochs,
-// [world] = CTA completion counter, [world + 1] = status (0 ok, 1 = a wait gave up).
+// The flag words and the closing handshake are those of gather_sink.cuh; epoch 0 takes the
+// epoch from the call counter there, which keeps the launch arguments constant and so lets
+// the call be replayed from a CUDA graph.
+constexpr int kPushUnroll = 4;
+
 __global__ void __launch_bounds__(256) allgather_push_kernel(PushArgs a) {
   const int64_t chunks_per_row = a.row_local / 16;
   const int64_t per_peer = a.M * chunks_per_row;
   const int64_t total = per_peer * a.world;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int p = (int)(i / per_peer);
-    const int64_t r = i - (int64_t)p * per_peer;
-    const int64_t m = r / chunks_per_row, c = r - m * chunks_per_row;
-    const uint4 v = *reinterpret_cast<const uint4*>(a.src + m * a.row_local + c * 16);
-    // start with the next rank so that the peers' links are loaded evenly
-    const int dst_rank = (a.rank + 1 + p) % a.world;
-    uint8_t* dst = a.peer_out[dst_rank] + m * a.row_full + (int64_t)a.rank * a.row_local + c * 16;
-    *reinterpret_cast<uint4*>(dst) = v;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // kPushUnroll independent 16-byte loads, then the stores: more bytes in flight per thread.
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += stride * kPushUnroll) {
+    uint4 v[kPushUnroll];
+    uint8_t* dst[kPushUnroll];
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      dst[u] = nullptr;
+      if (i < total) {
+        const int p = (int)(i / per_peer);
+        const int64_t r = i - (int64_t)p * per_peer;
+        const int64_t m = r / chunks_per_row, c = r - m * chunks_per_row;
+        v[u] = *reinterpret_cast<const uint4*>(a.src + m * a.row_local + c * 16);
+        // start with the next rank so that the peers' links are loaded evenly
+        const int dst_rank = (a.rank + 1 + p) % a.world;
+        dst[u] = a.peer_out[dst_rank] + m * a.row_full + (int64_t)a.rank * a.row_local + c * 16;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u)
+      if (dst[u] != nullptr) *reinterpret_cast<uint4*>(dst[u]) = v[u];
   }
   __shared__ int is_last;
   __threadfence_system();
   __syncthreads();
-  uint32_t* mine = a.peer_flags[a.rank];
-  if (threadIdx.x == 0) {
-    const unsigned old = atomicAdd(mine + a.world, 1u);
-    is_last = (old == gridDim.x - 1);
-  }
+  GatherSink g;
+  g.peer_out = nullptr;
+  g.peer_flags = a.peer_flags;
+  g.ld = 0; g.col0 = 0;
+  g.rank = a.rank; g.world = a.world; g.epoch = a.epoch;
+  if (threadIdx.x == 0) is_last = gather_cta_arrive(g, gridDim.x);
   __syncthreads();
   if (!is_last) return;
-  if (threadIdx.x == 0) mine[a.world] = 0;   // counter ready for the next launch
-  if (threadIdx.x < a.world) {
-    const int q = threadIdx.x;
-    uint32_t* theirs = a.peer_flags[q] + a.rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(a.epoch) : "memory");
-    const uint32_t* wait_on = mine + q;
-    uint64_t t0 = 0;
-    for (uint32_t spin = 0;; ++spin) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(wait_on) : "memory");
-      if ((int32_t)(v - a.epoch) >= 0) break;
-      if ((spin & 63u) == 63u) {
-        uint64_t now;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > 2000000000ull) { atomicExch(reinterpret_cast<int*>(mine + a.world + 1), 1); break; }
-        __nanosleep(200);
-      }
-    }
-  }
+  if (threadIdx.x < 32) gather_signal_and_wait(g, threadIdx.x);
 }
 
 }  // namespace
@@ -80,7 +78,7 @@ int allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem_byt
                    const void* peer_out, const void* peer_flags, int rank, int world,
                    uint32_t epoch, cudaStream_t st) {
   if (src == nullptr || peer_out == nullptr || peer_flags == nullptr) return NPB_ERR_INVALID_ARG;
-  if (world < 1 || world > 64 || rank < 0 || rank >= world || M < 0 || n_local <= 0) return NPB_ERR_INVALID_ARG;
+  if (world < 1 || world > 32 || rank < 0 || rank >= world || M < 0 || n_local <= 0) return NPB_ERR_INVALID_ARG;
   if (M == 0) return NPB_OK;
   const int64_t row_local = n_local * elem_bytes;
   if (row_local % 16 != 0 || !aligned_to(src, 16)) return NPB_ERR_ALIGNMENT;

@@ -8,6 +8,7 @@
 #include <map>
 
 #include "common.cuh"
+#include "gather_sink.cuh"
 
 namespace npb {
 
@@ -26,6 +27,10 @@ int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_
                  void*, cudaStream_t);
 
 int gemm_device_status(int*);
+int gemm_gather(const void*, const void*, const float*, int64_t, int64_t, int64_t, int, const GatherSink&,
+                cudaStream_t);
+int vq_gemv_gather(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
+                   const GatherSink&, cudaStream_t);
 int allgather_push(const void*, int64_t, int64_t, int64_t, const void*, const void*, int, int, uint32_t,
                    cudaStream_t);
 int vq_linear_static_scratch(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t,
@@ -200,6 +205,33 @@ int npb_allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem
                        uint32_t epoch, npb_stream_t stream) {
   return npb::allgather_push(src, M, n_local, elem_bytes, peer_out, peer_flags, rank, world, epoch,
                              static_cast<cudaStream_t>(stream));
+}
+
+static int to_sink(const npb_gather_sink* in, npb::GatherSink* out) {
+  if (in == nullptr) return NPB_ERR_INVALID_ARG;
+  out->peer_out = static_cast<void* const*>(in->peer_out);
+  out->peer_flags = static_cast<uint32_t* const*>(in->peer_flags);
+  out->ld = in->ld;
+  out->col0 = in->col0;
+  out->rank = in->rank;
+  out->world = in->world;
+  out->epoch = in->epoch;
+  return NPB_OK;
+}
+
+int npb_gemm_allgather(const void* x, const void* w, const float* bias, int64_t M, int64_t N_local,
+                       int64_t K, int dtype, const npb_gather_sink* sink, npb_stream_t stream) {
+  npb::GatherSink s;
+  if (int rc = to_sink(sink, &s)) return rc;
+  return npb::gemm_gather(x, w, bias, M, N_local, K, dtype, s, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_gemv_allgather(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
+                          int64_t N_local, int64_t K, const float* bias,
+                          const npb_gather_sink* sink, npb_stream_t stream) {
+  npb::GatherSink s;
+  if (int rc = to_sink(sink, &s)) return rc;
+  return npb::vq_gemv_gather(w, x, x_dtype, M, N_local, K, bias, s, static_cast<cudaStream_t>(stream));
 }
 
 int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }

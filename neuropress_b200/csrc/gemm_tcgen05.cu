@@ -27,6 +27,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "gather_sink.cuh"
 #include "tcgen05.cuh"
 
 namespace npb {
@@ -78,6 +79,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   FusedVq vq;
   FusedQ4 q4;
+  GatherSink sink;  // peer_out != null: y goes to every rank's buffer, then the handshake
 };
 
 template <int BN, int MT>
@@ -446,6 +448,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ================= epilogue: TMEM -> registers -> global =================
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) are this warp's
     T* y = static_cast<T*>(p.y);
+    // Fused all-gather: the tile goes to this rank's own [M, ld] buffer first (below, one
+    // output row per lane); once the four epilogue warps have stored it they re-read it
+    // row-wise and copy it to every peer with row-contiguous 16-byte stores -- NVLink carries
+    // those far better than the epilogue's own 16-bytes-per-row pattern.  The TMEM buffer is
+    // released before the copy, so the next tile's MMAs run under it.
+    const bool gathered = p.sink.peer_out != nullptr;
+    const int64_t ld = gathered ? p.sink.ld : p.N;
+    const int64_t col0 = gathered ? p.sink.col0 : 0;
+    if (gathered) y = static_cast<T*>(p.sink.peer_out[p.sink.rank]);
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
@@ -456,7 +467,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // warp-collective tcgen05.ld below is never reached by part of a warp.
       const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, kWaitTimeoutNs,
                                          BMODE == B_TMA ? 0u : 512u);
-      if (!__all_sync(0xffffffffu, got)) {
+      if (gathered) {
+        // The four warps meet at a named barrier further down, so they must leave together: a
+        // wait that gave up has raised the CTA's abort flag, which all of them read after this
+        // barrier (every warp reaches it, whatever its own wait returned).
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) {
+          atomicExch(&g_gemm_status, 3);
+          break;
+        }
+      } else if (!__all_sync(0xffffffffu, got)) {
         atomicExch(&g_gemm_status, 3);
         break;
       }
@@ -475,21 +495,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tmem_ld_wait();
           const int n0 = tn * BN + c * 32;
           if (m < p.M && n0 < p.N) {
-            T* dst = y + (size_t)m * p.N + n0;
-            const bool full = (n0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+            const int64_t off = (int64_t)m * ld + col0 + n0;
+            // destination bases are 16-byte aligned (checked on the host)
+            const bool full = (n0 + 32 <= p.N) && ((off * (int64_t)sizeof(T)) % 16 == 0);
             if (full) {
+              struct alignas(16) Out { T e[8]; } o[4];
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                struct alignas(16) Out { T e[8]; } o;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                   float f = __uint_as_float(v[q * 8 + e]);
                   if (p.bias) f += __ldg(p.bias + n0 + q * 8 + e);
-                  o.e[e] = from_f32<T>(f);
+                  o[q].e[e] = from_f32<T>(f);
                 }
-                reinterpret_cast<Out*>(dst)[q] = o;
               }
+              Out* dst = reinterpret_cast<Out*>(y + off);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) dst[q] = o[q];
             } else {
+              T* dst = y + off;
 #pragma unroll
               for (int e = 0; e < 32; ++e) {
                 if (n0 + e < p.N) {
@@ -505,6 +529,47 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      if (gathered && p.sink.world > 1) {
+        // copy the finished tile to the peers (N, ld and col0 are multiples of 8 elements)
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // all four warps' rows are stored
+        const int rows = min(MT * BM, p.M - tm * MT * BM);
+        const int cols = min(BN, p.N - tn * BN);
+        const int cpr = cols / 8;  // 16-byte chunks per row
+        const int64_t tile_off = (int64_t)(tm * MT * BM) * ld + col0 + (int64_t)tn * BN;
+        const int et = threadIdx.x - 64;  // 0..127 over the epilogue warps
+        for (int i0 = et; i0 < rows * cpr; i0 += 128 * 4) {
+          uint4 vv[4];
+          int64_t offs[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 128;
+            offs[u] = -1;
+            if (i < rows * cpr) {
+              const int r = i / cpr, c = i - r * cpr;
+              offs[u] = tile_off + (int64_t)r * ld + c * 8;
+              vv[u] = __ldcg(reinterpret_cast<const uint4*>(y + offs[u]));
+            }
+          }
+          for (int d = 1; d < p.sink.world; ++d) {
+            T* peer = static_cast<T*>(p.sink.peer_out[(p.sink.rank + d) % p.sink.world]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (offs[u] >= 0) *reinterpret_cast<uint4*>(peer + offs[u]) = vv[u];
+          }
+        }
+      }
+    }
+    if (gathered) {
+      // Fused all-gather: fence this CTA's peer stores, count the CTA in, and let the last
+      // CTA of the grid publish the flags and wait for the peers' slices.
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (warp == 2) {
+        int last = 0;
+        if (lane == 0) last = gather_cta_arrive(p.sink, gridDim.x) ? 1 : 0;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) gather_signal_and_wait(p.sink, lane);
+      }
     }
   } else {
     // ================= B decoders (fused modes only) =================
@@ -820,9 +885,10 @@ int check_gemm_common(const void* x, const void* y, int64_t M, int64_t N, int64_
 
 }  // namespace
 
-int gemm(const void* x, const void* w, const float* bias, void* y, int64_t M, int64_t N, int64_t K,
-         int dtype, cudaStream_t st) {
-  if (int rc = check_gemm_common(x, y, M, N, K, dtype)) return rc;
+namespace {
+int gemm_impl(const void* x, const void* w, const float* bias, void* y, int64_t M, int64_t N, int64_t K,
+              int dtype, const GatherSink* sink, cudaStream_t st) {
+  if (int rc = check_gemm_common(x, sink ? x : y, M, N, K, dtype)) return rc;
   if (M == 0 || N == 0) return NPB_OK;
   if (w == nullptr) return NPB_ERR_INVALID_ARG;
   if (!aligned_to(w, 16)) return NPB_ERR_ALIGNMENT;
@@ -830,7 +896,27 @@ int gemm(const void* x, const void* w, const float* bias, void* y, int64_t M, in
   p.bias = bias;
   p.y = y;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  if (sink) p.sink = *sink;
   return dtype == NPB_BF16 ? gemm_dense<__nv_bfloat16>(x, w, p, st) : gemm_dense<__half>(x, w, p, st);
+}
+}  // namespace
+
+int gemm(const void* x, const void* w, const float* bias, void* y, int64_t M, int64_t N, int64_t K,
+         int dtype, cudaStream_t st) {
+  return gemm_impl(x, w, bias, y, M, N, K, dtype, nullptr, st);
+}
+
+// Dense GEMM whose epilogue stores this rank's [M, N] result into columns [col0, col0 + N) of
+// every rank's [M, ld] buffer and closes with the all-gather handshake (gather_sink.cuh).
+int gemm_gather(const void* x, const void* w, const float* bias, int64_t M, int64_t N, int64_t K,
+                int dtype, const GatherSink& sink, cudaStream_t st) {
+  if (sink.peer_out == nullptr || sink.peer_flags == nullptr || sink.world < 1 ||
+      sink.world > kMaxGatherWorld || sink.rank < 0 || sink.rank >= sink.world || sink.ld < N ||
+      sink.col0 < 0 || sink.col0 + N > sink.ld)
+    return NPB_ERR_INVALID_ARG;
+  if (M == 0 || N == 0) return NPB_ERR_INVALID_ARG;  // every rank must run the handshake
+  if (N % 8 != 0 || sink.ld % 8 != 0 || sink.col0 % 8 != 0) return NPB_ERR_ALIGNMENT;  // 16-byte row pieces
+  return gemm_impl(x, w, bias, nullptr, M, N, K, dtype, &sink, st);
 }
 
 int vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,

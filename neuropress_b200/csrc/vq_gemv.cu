@@ -17,6 +17,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "gather_sink.cuh"
 
 namespace npb {
 namespace {
@@ -38,6 +39,7 @@ struct GemvArgs {
   void* y;
   int bits, res_bits, num_centroids, res_num_centroids, groups_per_codebook, n_codebooks;
   int M, N, K, Kp, G;
+  GatherSink sink;  // peer_out != null: y goes to every rank's buffer, then the handshake
 };
 
 template <typename T>
@@ -197,11 +199,45 @@ __global__ void __launch_bounds__(kThreads) vq_gemv_kernel(GemvArgs a) {
     for (int m = 0; m < MT; ++m) acc[m] = warp_sum(acc[m]);
     if (lane == 0) {
       const float b = a.bias ? __ldg(a.bias + n) : 0.f;
-      T* y = static_cast<T*>(a.y);
+      if (a.sink.peer_out == nullptr) {
+        T* y = static_cast<T*>(a.y);
 #pragma unroll
-      for (int m = 0; m < MT; ++m)
-        if (m < a.M) y[(size_t)m * a.N + n] = from_f32<T>(acc[m] + b);
+        for (int m = 0; m < MT; ++m)
+          if (m < a.M) y[(size_t)m * a.N + n] = from_f32<T>(acc[m] + b);
+      } else {
+        // fused all-gather: into this rank's own [M, ld] buffer first
+        T* y = static_cast<T*>(a.sink.peer_out[a.sink.rank]);
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+          if (m < a.M) y[(size_t)m * a.sink.ld + a.sink.col0 + n] = from_f32<T>(acc[m] + b);
+      }
     }
+  }
+  if (a.sink.peer_out != nullptr) {
+    // The last CTA to finish copies the whole [M, N] slice (a few KiB) to every peer with
+    // row-contiguous 16-byte stores, then runs the handshake.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = gather_cta_arrive(a.sink, gridDim.x) ? 1 : 0;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const T* mine = static_cast<const T*>(a.sink.peer_out[a.sink.rank]);
+    constexpr int EPC = 16 / (int)sizeof(T);  // elements per 16-byte chunk
+    const int cpr = a.N / EPC;
+    for (int i = tid; i < a.M * cpr; i += kThreads) {
+      const int m = i / cpr, c = i - m * cpr;
+      const size_t off = (size_t)m * a.sink.ld + a.sink.col0 + (size_t)c * EPC;
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine + off));
+      for (int d = 1; d < a.sink.world; ++d) {
+        T* peer = static_cast<T*>(a.sink.peer_out[(a.sink.rank + d) % a.sink.world]);
+        *reinterpret_cast<uint4*>(peer + off) = v;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (warp == 0) gather_signal_and_wait(a.sink, lane);
   }
 }
 
@@ -277,6 +313,7 @@ int run(const npb_vq_weight* w, GemvArgs a, cudaStream_t st) {
   int batch = 8;
   while (batch > 1 && (size_t)batch * Kp * sizeof(T) + res_bytes > (size_t)max_dynamic_smem() / 2)
     batch >>= 1;
+  if (a.sink.peer_out != nullptr && batch < M) return NPB_ERR_TOO_LARGE;  // one handshake per call
   for (int m0 = 0; m0 < M; m0 += batch) {
     GemvArgs b = a;
     b.M = (M - m0) < batch ? (M - m0) : batch;
@@ -289,12 +326,38 @@ int run(const npb_vq_weight* w, GemvArgs a, cudaStream_t st) {
 
 }  // namespace
 
+namespace {
+int vq_gemv_impl(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                 const float* bias, void* y, const GatherSink* sink, cudaStream_t st);
+}
+
 int vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
             const float* bias, void* y, cudaStream_t st) {
+  return vq_gemv_impl(w, x, x_dtype, M, N, K, bias, y, nullptr, st);
+}
+
+// GEMV whose result goes into columns [col0, col0 + N) of every rank's [M, ld] buffer, closed
+// by the all-gather handshake (gather_sink.cuh).  One launch, so M <= 8 rows must fit shared
+// memory together (NPB_ERR_TOO_LARGE otherwise).
+int vq_gemv_gather(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                   const float* bias, const GatherSink& sink, cudaStream_t st) {
+  if (sink.peer_out == nullptr || sink.peer_flags == nullptr || sink.world < 1 ||
+      sink.world > kMaxGatherWorld || sink.rank < 0 || sink.rank >= sink.world || sink.ld < N ||
+      sink.col0 < 0 || sink.col0 + N > sink.ld)
+    return NPB_ERR_INVALID_ARG;
+  if (M <= 0 || N <= 0) return NPB_ERR_INVALID_ARG;  // every rank must run the handshake
+  const int64_t epc = x_dtype == NPB_F32 ? 4 : 8;    // elements per 16-byte piece of a row
+  if (N % epc != 0 || sink.ld % epc != 0 || sink.col0 % epc != 0) return NPB_ERR_ALIGNMENT;
+  return vq_gemv_impl(w, x, x_dtype, M, N, K, bias, nullptr, &sink, st);
+}
+
+namespace {
+int vq_gemv_impl(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                 const float* bias, void* y, const GatherSink* sink, cudaStream_t st) {
   if (int rc = validate_vq(w, N, K)) return rc;
   if (M < 0 || M > NPB_GEMV_MAX_ROWS) return NPB_ERR_UNSUPPORTED;
   if (M == 0 || N == 0) return NPB_OK;
-  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (x == nullptr || (y == nullptr && sink == nullptr)) return NPB_ERR_INVALID_ARG;
   if (N >= (int64_t)1 << 31 || K >= (int64_t)1 << 24) return NPB_ERR_UNSUPPORTED;
   GemvArgs a{};
   a.packed = w->packed;
@@ -315,6 +378,7 @@ int vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64
   a.n_codebooks = w->cols_per_codebook > 0
                       ? (int)((K + w->cols_per_codebook - 1) / w->cols_per_codebook) : 1;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.G = (int)(K / w->vector_len);
+  if (sink) a.sink = *sink;
   switch (x_dtype) {
     case NPB_BF16: return run<__nv_bfloat16>(w, a, st);
     case NPB_F16: return run<__half>(w, a, st);
@@ -322,5 +386,6 @@ int vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64
     default: return NPB_ERR_UNSUPPORTED;
   }
 }
+}  // namespace
 
 }  // namespace npb

@@ -15,6 +15,7 @@ reference's plain form.
 
 from __future__ import annotations
 
+import ctypes
 import logging
 
 import torch
@@ -123,7 +124,8 @@ def vq_dequant(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
 
 
 def _vq_call(fn_name: str, x: torch.Tensor, packed: torch.Tensor, centroids: torch.Tensor,
-             bits: int, out_features: int | None, bias: torch.Tensor | None, ext: dict) -> torch.Tensor:
+             bits: int, out_features: int | None, bias: torch.Tensor | None, ext: dict,
+             gather=None) -> torch.Tensor:
     ext = _vq_ext(ext)
     if x.dim() != 2:
         raise RuntimeError(f"{fn_name}: x must be 2-D [M, K].")
@@ -135,6 +137,15 @@ def _vq_call(fn_name: str, x: torch.Tensor, packed: torch.Tensor, centroids: tor
     n = out_features if out_features is not None else _infer_n(packed, bits, k, vl)
     w = _cabi.vq_struct(packed, centroids, bits, **ext)
     b = _bias_f32(bias, n, x.device)
+    if gather is not None:
+        # fused all-gather: the kernel stores into every rank's [M, N_full] buffer
+        sink, out = gather.begin(m, n, x.dtype)
+        with torch.cuda.device(x.device):
+            rc = _launch(fn_name + "_allgather", getattr(lib, fn_name + "_allgather"), w, x.data_ptr(),
+                         _cabi.dtype_code(x.dtype), m, n, k, None if b is None else b.data_ptr(),
+                         ctypes.byref(sink), _cabi.stream_ptr())
+        _cabi.check(rc, fn_name + "_allgather")
+        return out
     y = torch.empty((m, n), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         rc = _launch(fn_name, getattr(lib, fn_name), w, x.data_ptr(), _cabi.dtype_code(x.dtype), m, n, k,
@@ -145,10 +156,13 @@ def _vq_call(fn_name: str, x: torch.Tensor, packed: torch.Tensor, centroids: tor
 
 
 def vq_gemv(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
-            out_features: int | None = None, bias: torch.Tensor | None = None, **ext) -> torch.Tensor:
+            out_features: int | None = None, bias: torch.Tensor | None = None, gather=None,
+            **ext) -> torch.Tensor:
     """Fused index-decode GEMV, ``x`` is ``[M, K]`` with ``M <= GEMV_MAX_ROWS``; fp16, bf16 or
-    fp32 activations; output in ``x.dtype``."""
-    return _vq_call("npb_vq_gemv", x, packed_indices, centroids, bits, out_features, bias, ext)
+    fp32 activations; output in ``x.dtype``.  With ``gather`` (a ``sharding.PushGather``) the
+    kernel writes this rank's columns into every rank's buffer and the full ``[M, N]`` comes
+    back (``npb_vq_gemv_allgather``)."""
+    return _vq_call("npb_vq_gemv", x, packed_indices, centroids, bits, out_features, bias, ext, gather)
 
 
 def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
@@ -210,9 +224,11 @@ def vq_linear_wmma(x: torch.Tensor, packed_indices: torch.Tensor, centroids: tor
 # ---------------------------------------------------------------------------
 
 
-def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gather=None) -> torch.Tensor:
     """``x[M,K] @ w[N,K].T (+ bias)`` on the tcgen05 tensor cores, bf16 / fp16, fp32
-    accumulate.  Stands in for ``F.linear`` after the decode (np_vq_linear.py:1148)."""
+    accumulate.  Stands in for ``F.linear`` after the decode (np_vq_linear.py:1148).  With
+    ``gather`` (a ``sharding.PushGather``) the epilogue writes this rank's columns into every
+    rank's buffer and the full ``[M, N]`` comes back (``npb_gemm_allgather``)."""
     if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
         raise RuntimeError("gemm: expected x [M, K] and w [N, K].")
     if x.dtype != w.dtype:
@@ -222,6 +238,14 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> 
     m, k = x.shape
     n = w.shape[0]
     b = _bias_f32(bias, n, x.device)
+    if gather is not None:
+        sink, out = gather.begin(m, n, x.dtype)
+        with torch.cuda.device(x.device):
+            rc = _launch("npb_gemm_allgather", lib.npb_gemm_allgather, x.data_ptr(), w.data_ptr(),
+                         None if b is None else b.data_ptr(), m, n, k, _cabi.dtype_code(x.dtype),
+                         ctypes.byref(sink), _cabi.stream_ptr())
+        _cabi.check(rc, "gemm_allgather")
+        return out
     y = torch.empty((m, n), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         rc = _launch("npb_gemm", lib.npb_gemm, x.data_ptr(), w.data_ptr(), None if b is None else b.data_ptr(),

@@ -283,8 +283,13 @@ class NPVQLinear(nn.Module):
                          shape=(self.out_features, self.in_features), meta=dict(self._qtensor_meta))
 
     # ------------------------------------------------------------------ forward
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """Route by row count exactly as the reference does (:1014-1058)."""
+    def forward(self, x: torch.Tensor, gather=None) -> torch.Tensor:
+        """Route by row count exactly as the reference does (:1014-1058).
+
+        ``gather`` (not in the reference) is a ``sharding.PushGather``: this module then holds
+        an out-feature shard, and the result is the all-gathered ``[..., N_full]``.  Where the
+        band's kernel can store into the peers' buffers itself it does (fused all-gather);
+        otherwise the local result is pushed by a separate kernel."""
         if self.column_perm is not None:
             x = x[..., self.column_perm]
         if self.backend in _FUSED_BACKENDS:
@@ -292,14 +297,14 @@ class NPVQLinear(nn.Module):
             if m > _fused_max_tokens(self.backend):
                 skip_tile = _LUT_SKIPS_TILE_BAND and self.backend == VQBackend.CUDA_LUT
                 if not skip_tile and m <= _TRITON_MAX_TOKENS:
-                    return self._forward_triton(x)
-                return self._forward_dequant_gemm(x)
+                    return self._forward_triton(x, gather)
+                return self._forward_dequant_gemm(x, gather)
         if self.backend == VQBackend.CUDA_LUT:
-            return self._forward_cuda_lut(x)
+            return self._forward_cuda_lut(x, gather)
         if self.backend == VQBackend.CUDA_WMMA:
-            return self._forward_cuda_wmma(x)
+            return self._forward_cuda_wmma(x, gather)
         if self.backend == VQBackend.CUDA:
-            return self._forward_cuda(x)
+            return self._forward_cuda(x, gather)
         raise NotImplementedError(
             f"backend {self.backend.value!r} is not implemented by this package: only the CUDA "
             "backends (cuda, cuda_wmma, cuda_lut) exist here; there is no eager, compiled or "
@@ -338,46 +343,52 @@ class NPVQLinear(nn.Module):
         return x.reshape(-1, self.in_features).contiguous(), leading
 
     # -- band (a): fused index-decode GEMV
-    def _forward_gemv(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_gemv(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         from .. import kernels
 
         x2, leading = self._flat(x)
+        fused = gather is not None and gather.accepts(x2.shape[0], x2.dtype)
         y = kernels.vq_gemv(x2, self.packed_indices, self.proxy.centroids, self.bits,
-                            self.out_features, self._bias32(), **self._ext())
-        return y.reshape(*leading, self.out_features)
+                            self.out_features, self._bias32(), gather=gather if fused else None,
+                            **self._ext())
+        if gather is not None and not fused:
+            y = gather(y)
+        return y.reshape(*leading, y.shape[-1])
 
-    def _forward_cuda(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_cuda(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """Fused GEMV, fp16 / bf16 / fp32 activations natively (reference :1173-1187)."""
-        return self._forward_gemv(x)
+        return self._forward_gemv(x, gather)
 
-    def _forward_cuda_wmma(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_cuda_wmma(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """Reference :1250-1267.  The reference casts fp32 activations to fp16 first; the GEMV
         here accumulates in fp32 from any activation dtype, so no cast is needed."""
-        return self._forward_gemv(x)
+        return self._forward_gemv(x, gather)
 
-    def _forward_cuda_lut(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_cuda_lut(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """Reference :1189-1248 builds an ``[M, G, NC]`` table in global memory and gathers
         from it, which loses to decoding at every row count (:75-79).  Here ``cuda_lut`` layers
         (large codebooks, large ``N / NC``) run the same fused GEMV, which gathers 16-byte
         centroids through L1 / L2 instead."""
-        return self._forward_gemv(x)
+        return self._forward_gemv(x, gather)
 
     # -- band (b): tile-decode tensor-core GEMM (the reference's Triton band)
-    def _forward_triton(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_triton(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """Tile-decode GEMM on the tcgen05 tensor cores; the method keeps the reference's
         name (:1097-1125).  Shapes or dtypes the kernel does not take go to decode + GEMM."""
         from .. import kernels
 
         if (not kernels.VQ_TILE_DECODE_GEMM or x.dtype not in (torch.bfloat16, torch.float16)
                 or self.vector_len != 8 or self.in_features % 64):
-            return self._forward_dequant_gemm(x)
+            return self._forward_dequant_gemm(x, gather)
         x2, leading = self._flat(x)
         y = kernels.vq_gemm_fused(x2, self.packed_indices, self.proxy.centroids, self.bits,
                                   self.out_features, self._bias32(), **self._ext())
-        return y.reshape(*leading, self.out_features)
+        if gather is not None:
+            y = gather(y)
+        return y.reshape(*leading, y.shape[-1])
 
     # -- band (c): one-pass decode + dense tensor-core GEMM
-    def _forward_dequant_gemm(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_dequant_gemm(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """Decode the weight once into a temporary ``[N, K]`` tensor in the activation dtype
         and run the dense GEMM (reference :1127-1148).  fp32 activations are computed in fp16,
         as the reference's tensor-core path does (:1254-1256)."""
@@ -389,8 +400,12 @@ class NPVQLinear(nn.Module):
         x2, leading = self._flat(x)
         w = kernels.vq_dequant(self.packed_indices, self.proxy.centroids, self.bits,
                                self.out_features, self.in_features, x2.dtype, **self._ext())
-        y = kernels.gemm(x2, w, self._bias32()).reshape(*leading, self.out_features)
-        return y.to(orig) if y.dtype != orig else y
+        fused = gather is not None and orig == x2.dtype and gather.accepts(x2.shape[0], x2.dtype)
+        y = kernels.gemm(x2, w, self._bias32(), gather=gather if fused else None)
+        y = y.to(orig) if y.dtype != orig else y
+        if gather is not None and not fused:
+            y = gather(y)
+        return y.reshape(*leading, y.shape[-1])
 
     def extra_repr(self) -> str:
         perm = ", perm=True" if self.column_perm is not None else ""

@@ -58,11 +58,27 @@ def _worker(rank: int, world: int, port: int, q) -> None:
             assert y.shape == (rows, 512)
             assert_output_close(y, ref, torch.bfloat16)
         layer.enable_push_gather(max_rows=300, dtype=torch.bfloat16, device=dev)
-        for it in range(3):                           # push gather, buffers alternate
+        for it in range(3):                           # fused all-gather, buffers alternate
             for rows, (x, ref) in refs.items():
                 y = layer(x)
                 assert y.shape == (rows, 512)
                 assert_output_close(y, ref, torch.bfloat16)
+        for rows, (x, ref) in refs.items():           # stand-alone push kernel
+            y = layer.push(layer.local(x))
+            assert y.shape == (rows, 512)
+            assert_output_close(y, ref, torch.bfloat16)
+        # CUDA-graph replay: the launch arguments are constant, the epoch lives on the device
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                outs = [layer(refs[rows][0]) for rows in (2, 300)]   # an even number of calls
+            for _ in range(3):
+                graph.replay()
+            side.synchronize()
+        for rows, y in zip((2, 300), outs):
+            assert_output_close(y, refs[rows][1], torch.bfloat16)
         assert layer.push.status() == 0
     except Exception as exc:  # report instead of hanging the peer
         ok, msg = False, repr(exc)[:500]

@@ -92,9 +92,9 @@ def _layer_with_spies(monkeypatch, backend, fused_max=16, lut_max=16, tile_max=0
     calls = []
     fused = {Backend.CUDA_WMMA: "_forward_cuda_wmma", Backend.CUDA_LUT: "_forward_cuda_lut",
              Backend.CUDA: "_forward_cuda"}[backend]
-    monkeypatch.setattr(layer, fused, lambda x: calls.append("fused") or x[..., :16])
-    monkeypatch.setattr(layer, "_forward_dequant_gemm", lambda x: calls.append("dense") or x[..., :16])
-    monkeypatch.setattr(layer, "_forward_triton", lambda x: calls.append("tile") or x[..., :16])
+    monkeypatch.setattr(layer, fused, lambda x, gather=None: calls.append("fused") or x[..., :16])
+    monkeypatch.setattr(layer, "_forward_dequant_gemm", lambda x, gather=None: calls.append("dense") or x[..., :16])
+    monkeypatch.setattr(layer, "_forward_triton", lambda x, gather=None: calls.append("tile") or x[..., :16])
     return layer, calls
 
 
@@ -131,7 +131,7 @@ def test_column_permutation_is_applied_before_dispatch(monkeypatch):
     lin.weight.qscheme.column_permutation = perm
     layer = NPVQLinear.from_qtensor_linear(lin, VQProxy(lin.weight.qscheme.centroids), backend="cuda")
     seen = []
-    monkeypatch.setattr(layer, "_forward_cuda", lambda x: seen.append(x) or x[..., :16])
+    monkeypatch.setattr(layer, "_forward_cuda", lambda x, gather=None: seen.append(x) or x[..., :16])
     x = torch.randn(1, 32)
     layer(x)
     assert torch.equal(seen[0], x[..., perm])
