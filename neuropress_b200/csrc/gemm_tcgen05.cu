@@ -537,11 +537,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int cpr = cols / 8;  // 16-byte chunks per row
         const int64_t tile_off = (int64_t)(tm * MT * BM) * ld + col0 + (int64_t)tn * BN;
         const int et = threadIdx.x - 64;  // 0..127 over the epilogue warps
-        for (int i0 = et; i0 < rows * cpr; i0 += 128 * 4) {
-          uint4 vv[4];
-          int64_t offs[4];
+        constexpr int U = 8;  // 16-byte pieces in flight per thread
+        for (int i0 = et; i0 < rows * cpr; i0 += 128 * U) {
+          uint4 vv[U];
+          int64_t offs[U];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < U; ++u) {
             const int i = i0 + u * 128;
             offs[u] = -1;
             if (i < rows * cpr) {
@@ -553,7 +554,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int d = 1; d < p.sink.world; ++d) {
             T* peer = static_cast<T*>(p.sink.peer_out[(p.sink.rank + d) % p.sink.world]);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < U; ++u)
               if (offs[u] >= 0) *reinterpret_cast<uint4*>(peer + offs[u]) = vv[u];
           }
         }
