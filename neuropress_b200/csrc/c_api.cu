@@ -80,7 +80,8 @@ int blocks_per_sm(const void* kernel, int threads, size_t smem, int* per_sm) {
   const auto key = std::make_tuple(dev, kernel, smem);
   auto it = cache.find(key);
   if (it == cache.end()) {
-    if (smem > 48 * 1024)
+    // opt in as soon as dynamic + (small) static shared memory can pass the 48 KiB default
+    if (smem + 1024 > 48 * 1024)
       NPB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int n = 0;
     NPB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem));

@@ -39,6 +39,7 @@ struct GemvArgs {
   void* y;
   int bits, res_bits, num_centroids, res_num_centroids, groups_per_codebook, n_codebooks;
   int M, N, K, Kp, G;
+  int res_rep;  // copies of the residual table in shared memory (1 or 8, see the kernel)
   GatherSink sink;  // peer_out != null: y goes to every rank's buffer, then the handshake
 };
 
@@ -87,7 +88,12 @@ __global__ void __launch_bounds__(kThreads) vq_gemv_kernel(GemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   T* xs = reinterpret_cast<T*>(smem);
   __half* rcs = reinterpret_cast<__half*>(smem + (size_t)MT * a.Kp * sizeof(T));
-  __half* cbs = rcs + (a.res_packed ? a.res_num_centroids * VL : 0);
+  __half* cbs = rcs + (a.res_packed ? a.res_num_centroids * VL * a.res_rep : 0);
+  // With res_rep == 8 entry e is stored eight times, at 16-byte slots 8 e .. 8 e + 7, and a lane
+  // reads slot 8 e + (lane & 7): the eight lanes that share a pass of a 128-bit shared-memory
+  // load then always hit eight different bank groups, so the random gather is conflict-free.
+  const int rep_shift = a.res_rep == 8 ? 3 : 0;
+  const int rep_lane = (threadIdx.x & 7) & (a.res_rep - 1);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool has_res = a.res_packed != nullptr;
 
@@ -105,10 +111,16 @@ __global__ void __launch_bounds__(kThreads) vq_gemv_kernel(GemvArgs a) {
       }
     }
     if (has_res) {
-      const int nw = a.res_num_centroids * VL / 2;
-      for (int t = tid; t < nw; t += kThreads)
-        reinterpret_cast<uint32_t*>(rcs)[t] =
-            __ldg(reinterpret_cast<const uint32_t*>(a.res_centroids) + t);
+      if (a.res_rep == 8) {  // VL == 8 here: one entry is one 16-byte word
+        const int nw = a.res_num_centroids * 8;
+        for (int t = tid; t < nw; t += kThreads)
+          reinterpret_cast<uint4*>(rcs)[t] = __ldg(reinterpret_cast<const uint4*>(a.res_centroids) + (t >> 3));
+      } else {
+        const int nw = a.res_num_centroids * VL / 2;
+        for (int t = tid; t < nw; t += kThreads)
+          reinterpret_cast<uint32_t*>(rcs)[t] =
+              __ldg(reinterpret_cast<const uint32_t*>(a.res_centroids) + t);
+      }
     }
     if constexpr (CB_SMEM) {
       const int nw = a.n_codebooks * a.num_centroids * VL / 8;  // 16-byte words
@@ -153,7 +165,7 @@ __global__ void __launch_bounds__(kThreads) vq_gemv_kernel(GemvArgs a) {
         for (int i = 0; i < 8; ++i) {
           float w[8];
           Half8 rv = cv[i];
-          if (has_res) rv = reinterpret_cast<const Half8*>(rcs)[ridx[i]];
+          if (has_res) rv = reinterpret_cast<const Half8*>(rcs)[(ridx[i] << rep_shift) + rep_lane];
           weight_f32<T, 4>(cv[i].h, has_res, rv.h, has_scale, s2, w);
           const int pos = swz(c * 8 + i);
 #pragma unroll
@@ -276,13 +288,9 @@ int run_rows(const npb_vq_weight* w, GemvArgs a, cudaStream_t st) {
   a.Kp = (a.K + 63) / 64 * 64;
   const int mt = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
   const size_t x_bytes = (size_t)mt * a.Kp * sizeof(T);
-  const size_t res_bytes = a.res_packed ? (size_t)a.res_num_centroids * VL * 2 : 0;
+  size_t res_bytes = a.res_packed ? (size_t)a.res_num_centroids * VL * 2 : 0;
   const size_t cb_bytes = (size_t)a.n_codebooks * a.num_centroids * VL * 2;
   const size_t cap = (size_t)max_dynamic_smem();
-  if (x_bytes + res_bytes > cap) return NPB_ERR_TOO_LARGE;
-  const bool cb_smem = cb_bytes <= (size_t)kSmemCodebookMax && x_bytes + res_bytes + cb_bytes <= cap &&
-                       aligned_to(a.centroids, 16) && (res_bytes % 16 == 0);
-  const size_t smem = x_bytes + res_bytes + (cb_smem ? cb_bytes : 0);
 
   // Vector index path: VL 8, whole 8-index chunks per row, aligned streams, 8-bit residual.
   int vbits = 0;
@@ -292,6 +300,16 @@ int run_rows(const npb_vq_weight* w, GemvArgs a, cudaStream_t st) {
       (!a.res_packed || (a.res_bits == 8 && aligned_to(a.res_packed, 8) &&
                          aligned_to(a.res_centroids, 16))))
     vbits = a.bits;
+  // Replicate a small residual table eight-fold (conflict-free gathers); vector path only.
+  a.res_rep = 1;
+  if (vbits != 0 && a.res_packed && res_bytes * 8 <= 32 * 1024 && x_bytes + res_bytes * 8 <= cap) {
+    a.res_rep = 8;
+    res_bytes *= 8;
+  }
+  if (x_bytes + res_bytes > cap) return NPB_ERR_TOO_LARGE;
+  const bool cb_smem = cb_bytes <= (size_t)kSmemCodebookMax && x_bytes + res_bytes + cb_bytes <= cap &&
+                       aligned_to(a.centroids, 16) && (res_bytes % 16 == 0);
+  const size_t smem = x_bytes + res_bytes + (cb_smem ? cb_bytes : 0);
   if (VL == 8) {
     switch (vbits) {
       case 16: return launch_mt<T, 8, 16>(a, mt, cb_smem, smem, st);

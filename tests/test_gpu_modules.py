@@ -136,3 +136,36 @@ def test_full_size_layer_properties():
     from neuropress_b200 import _cabi
 
     assert _cabi.gemm_device_status() == 0
+
+
+def test_70b_shaped_layer_properties():
+    """Largest layer shape of the 70B-shaped configuration (28672 x 8192, one 65536-entry codebook,
+    uint16 indices: 58.7 M indices, 117 MB of index bytes): spot rows of the decode against the
+    oracle, unit-vector GEMV = weight column, band agreement, and the eight out-feature shards
+    reproducing their rows of the full decode bit for bit."""
+    from neuropress_b200 import _cabi, kernels
+    from neuropress_b200.sharding import shard_vq_linear
+
+    N, K, G_ = 28672, 8192, 8192 // 8
+    d = make_vq_layer(N, K, num_centroids=65536, bits=16, seed=70)
+    layer = NPVQLinear(VQProxy(d.centroids), d.packed, 16, N, K, 8, backend="auto")
+    w = kernels.vq_dequant(d.packed.to(DEV), d.centroids.to(DEV), 16, N, K, torch.bfloat16)
+    for r in (0, 1, 12345, N - 1):
+        sl = slice(r * G_ * 2, (r + 1) * G_ * 2)
+        ref = oracle.vq_decode(d.packed[sl], d.centroids, 16, 1, K, torch.bfloat16)
+        assert torch.equal(w[r].cpu(), ref[0])
+    for rank in (0, 3, 7):   # shards of an 8-way split decode to exactly their rows
+        shard = shard_vq_linear(layer, 8, rank)
+        ws = kernels.vq_dequant(shard.packed_indices.to(DEV), d.centroids.to(DEV), 16, N // 8, K,
+                                torch.bfloat16)
+        assert torch.equal(ws, w[rank * (N // 8):(rank + 1) * (N // 8)])
+    layer.proxy.to(DEV)
+    layer = layer.to(DEV)
+    e = torch.zeros(1, K, dtype=torch.bfloat16, device=DEV)
+    e[0, 4321] = 1
+    assert torch.equal(layer(e)[0], w[:, 4321])
+    x = make_activations(32, K, torch.bfloat16, seed=9).to(DEV)   # the batch-32 decode of that config
+    ref = x.double() @ w.double().T
+    assert_output_close(layer(x), ref, torch.bfloat16)
+    assert_output_close(layer(x[:2].contiguous()), ref[:2], torch.bfloat16)
+    assert _cabi.gemm_device_status() == 0

@@ -113,3 +113,43 @@ def test_all_gather_assembly_two_gloo_ranks():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == [(0, True), (1, True)]
+
+
+class _FakeGather:
+    """Stands in for PushGather on CPU: records how the sharded layer used it."""
+
+    def __init__(self, fused_rows: int, world: int = 2) -> None:
+        self.fused_rows, self.world, self.dtype, self.max_rows = fused_rows, world, torch.float32, 1 << 20
+        self.calls = []
+
+    def accepts(self, m: int, dtype: torch.dtype) -> bool:
+        return m <= self.fused_rows
+
+    def __call__(self, y: torch.Tensor) -> torch.Tensor:
+        self.calls.append(("push", tuple(y.shape)))
+        return torch.cat([y] * self.world, dim=-1)
+
+
+def test_sharded_layer_hands_the_gather_to_the_shard_kernels(monkeypatch):
+    """With a push gather enabled the shard's forward receives it (so that its kernels can store
+    to the peers themselves); a kernel that cannot fuse gets the stand-alone push instead."""
+    from neuropress_b200 import kernels
+
+    d = make_vq_layer(32, 64, num_centroids=16, bits=4, seed=1)
+    full = NPVQLinear(VQProxy(d.centroids), d.packed, 4, 32, 64, 8, backend="cuda")
+    layer = ShardedLinear.from_layer(full, 0, 2)
+    fake = _FakeGather(fused_rows=1)
+    layer.push = fake
+    seen = []
+
+    def fake_gemv(x, packed, centroids, bits, n, bias, gather=None, **ext):
+        seen.append(("gemv", x.shape[0], gather is fake))
+        if gather is not None:
+            return torch.zeros(x.shape[0], n * 2)       # the kernel filled the full-width buffer
+        return torch.zeros(x.shape[0], n)
+
+    monkeypatch.setattr(kernels, "vq_gemv", fake_gemv)
+    y = layer(torch.zeros(1, 64))                        # 1 row: fused
+    assert y.shape == (1, 32) and seen[-1] == ("gemv", 1, True) and fake.calls == []
+    y = layer(torch.zeros(2, 1, 64))                     # 2 rows: kernel cannot fuse -> push after it
+    assert y.shape == (2, 1, 32) and seen[-1] == ("gemv", 2, False) and fake.calls == [("push", (2, 16))]
