@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "gather_sink.cuh"
+#include "q4_math.cuh"
 #include "tcgen05.cuh"
 
 namespace npb {
@@ -244,31 +245,6 @@ __device__ __forceinline__ void q4_fetch(Q4Item<RPL>& it, const FusedQ4& p, int 
   }
 }
 
-// Packed fp32 (two lanes per instruction, sm_100), round-to-nearest, one rounding each.
-__device__ __forceinline__ float2 fsub2(const float2 a, const float2 b) {
-  uint64_t d;
-  asm("sub.rn.f32x2 %0, %1, %2;"
-      : "=l"(d)
-      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
-  return reinterpret_cast<const float2&>(d);
-}
-__device__ __forceinline__ float2 fmul2(const float2 a, const float2 b) {
-  uint64_t d;
-  asm("mul.rn.f32x2 %0, %1, %2;"
-      : "=l"(d)
-      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
-  return reinterpret_cast<const float2&>(d);
-}
-
-__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-__device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
-  const __half2 v = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
-
 // (q - z) * s in fp32 with one rounding per operation, exactly as the one-pass decode does,
 // two elements per instruction (packed fp32).  0x4B000000 | q is the float 2^23 + q, so
 // subtracting 2^23 yields q without an int-to-float conversion; for a symmetric weight
@@ -279,26 +255,9 @@ __device__ __forceinline__ void q4_emit_half(const uint4& codes, __half sh, __ha
   const float s = valid ? __half2float(sh) : 0.f;
   const float z = __half2float(zh);
   const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
-  const float2 s2 = make_float2(s, s);
-  const float2 m2 = ASYM ? make_float2(8388608.f, 8388608.f) : make_float2(8388616.f, 8388616.f);
-  const float2 z2 = make_float2(z, z);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const uint32_t lo = words[j] & 0x0f0f0f0fu;         // elements 0, 2, 4, 6 (one per byte)
-    const uint32_t hi = (words[j] >> 4) & 0x0f0f0f0fu;  // elements 1, 3, 5, 7
-    uint32_t o[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      // byte e of lo / hi into the low byte of 0x4B000000
-      float2 q = make_float2(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7650 + e)),
-                             __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7650 + e)));
-      q = fsub2(q, m2);
-      if (ASYM) q = fsub2(q, z2);
-      q = fmul2(q, s2);
-      o[e] = pack2(q.x, q.y, T());
-    }
-    st_shared_v4(row_addr + (((half * 4 + j) ^ sw) << 4), make_uint4(o[0], o[1], o[2], o[3]));
-  }
+  for (int j = 0; j < 4; ++j)
+    st_shared_v4(row_addr + (((half * 4 + j) ^ sw) << 4), q4_word_to_chunk<T, ASYM>(words[j], s, z));
 }
 
 // row0: tile row of the warp's first row (n0 = tile's first W row + row0).

@@ -16,6 +16,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "q4_math.cuh"
 
 namespace npb {
 
@@ -65,9 +66,61 @@ q_decode_kernel(const uint8_t* __restrict__ codes, const __half* __restrict__ sc
   }
 }
 
+// 4-bit decode to a 16-bit type, the large-batch path: a thread converts four 8-value chunks
+// that lie 256 chunks apart, so every warp-wide code load (4 bytes per lane) and store (16
+// bytes per lane) is contiguous; nibble -> fp32 by byte-permute, (q - z) * s in packed fp32
+// (q4_math.cuh), 32-bit index arithmetic, group index by shift when the group is a power of
+// two.  HBM bytes: codes + scales (+ zero points) in, N*K*2 out; the kernel is write-bound.
+constexpr int kDec4Unroll = 4;
+
+template <typename T, bool ASYM>
+__global__ void __launch_bounds__(kDecThreads)
+q4_decode16_kernel(const uint32_t* __restrict__ codes, const __half* __restrict__ scale,
+                   const __half* __restrict__ zp, uint4* __restrict__ out, uint32_t n_chunks,
+                   uint32_t chunks_per_group, int cpg_shift) {
+  const uint32_t base = blockIdx.x * (kDecThreads * kDec4Unroll) + threadIdx.x;
+  uint32_t word[kDec4Unroll];
+  __half s[kDec4Unroll], z[kDec4Unroll];
+#pragma unroll
+  for (int u = 0; u < kDec4Unroll; ++u) {
+    const uint32_t c = base + u * kDecThreads;
+    // chunks past the end read chunk 0 (always mapped) and are not stored
+    const uint32_t cc = c < n_chunks ? c : 0u;
+    const uint32_t g = cpg_shift >= 0 ? cc >> cpg_shift : cc / chunks_per_group;
+    word[u] = __ldg(codes + cc);
+    s[u] = __ldg(scale + g);
+    z[u] = __ldg(zp + g);  // symmetric weights pass the scale pointer here: a mapped address
+  }
+#pragma unroll
+  for (int u = 0; u < kDec4Unroll; ++u) {
+    const uint32_t c = base + u * kDecThreads;
+    if (c < n_chunks)
+      out[c] = q4_word_to_chunk<T, ASYM>(word[u], __half2float(s[u]), __half2float(z[u]));
+  }
+}
+
 template <typename T>
 int launch_decode(const npb_q_weight* w, int64_t N, int64_t K, T* out, cudaStream_t st) {
   const int64_t n_chunks = N * K / 8;
+  if constexpr (sizeof(T) == 2) {
+    if (w->nbits == 4 && n_chunks < ((int64_t)1 << 31) && aligned_to(w->codes, 4) && aligned_to(out, 16)) {
+      const uint32_t cpg = (uint32_t)(w->group_size / 8);
+      const int shift = (cpg & (cpg - 1)) == 0 ? __builtin_ctz(cpg) : -1;
+      const uint32_t per_block = kDecThreads * kDec4Unroll;
+      const uint32_t blocks = (uint32_t)((n_chunks + per_block - 1) / per_block);
+      const uint32_t* c32 = reinterpret_cast<const uint32_t*>(w->codes);
+      const __half* sc = static_cast<const __half*>(w->scale);
+      uint4* o = reinterpret_cast<uint4*>(out);
+      if (w->zero_point)
+        q4_decode16_kernel<T, true><<<blocks, kDecThreads, 0, st>>>(
+            c32, sc, static_cast<const __half*>(w->zero_point), o, (uint32_t)n_chunks, cpg, shift);
+      else
+        q4_decode16_kernel<T, false><<<blocks, kDecThreads, 0, st>>>(c32, sc, sc, o, (uint32_t)n_chunks,
+                                                                      cpg, shift);
+      NPB_LAUNCH_CHECK();
+      return NPB_OK;
+    }
+  }
   const int64_t blocks = (n_chunks + kDecThreads - 1) / kDecThreads;
   if (blocks >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
   const __half* s = static_cast<const __half*>(w->scale);

@@ -319,13 +319,13 @@ def q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point=None, bias=None
     return _q_call("npb_q_gemm_fused", x, w_pack, scale, nbits, group_size, zero_point, bias)
 
 
-# Row count up to which q_linear re-decodes the weight inside the GEMM; above it the weight is
-# decoded once and the dense GEMM runs (the tile-dequant GEMM repeats the decode per 384 rows).
+# Whether q_linear's mid band (9..Q_FUSED_MAX_ROWS rows) runs the tile-dequant GEMM
+# (``npb_q_gemm_fused``); when False it decodes once and runs the dense GEMM.  Off: with the
+# packed-fp32 decode kernel the pair is as fast or faster on every shape measured on a B200
+# (14336 x 4096: 50 / 56 / 74 us at 128 / 256 / 384 rows against 51 / 59 / 82 us fused;
+# 4096 x 4096: 32 us against 50 us, the fused kernel having only 32 CTAs there).
+Q_TILE_DEQUANT_GEMM = False
 Q_FUSED_MAX_ROWS = 384
-# The tile-dequant GEMM runs one CTA per 128 output features, so it only pays when those CTAs
-# cover most of the GPU (measured on 148 SMs: 14336 features, 128 rows: 51 us against 63 us
-# for decode + GEMM; 4096 features: 50 us against 32 us).
-Q_FUSED_MIN_TILES = 96
 
 
 def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: int,
@@ -333,16 +333,16 @@ def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: 
              bias: torch.Tensor | None = None) -> torch.Tensor:
     """Drop-in for the reference's ``q_linear`` (kernels/__init__.py:109-151): ``x`` is
     ``[..., K]``, output ``[..., N]`` in ``x.dtype``.  The reference runs one GEMV kernel for
-    every row count (q4_linear.cu:137-140); here rows are banded: GEMV, tile-dequant GEMM,
-    then decode once + dense GEMM."""
+    every row count (q4_linear.cu:137-140); here rows are banded: GEMV up to 8 rows, then
+    decode once + dense GEMM (or, opt-in, the tile-dequant GEMM for the mid band)."""
     k = w_pack.shape[1] * (8 // nbits)
     m = x.numel() // max(k, 1)
     if m <= GEMV_MAX_ROWS:
         return q_gemv(x, w_pack, scale, nbits, group_size, zero_point, bias)
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("q_linear: more than 8 rows need fp16 or bf16 activations.")
-    if (m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0 and group_size % 32 == 0
-            and (w_pack.shape[0] + 127) // 128 >= Q_FUSED_MIN_TILES):
+    if (Q_TILE_DEQUANT_GEMM and m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0
+            and group_size % 32 == 0):
         return q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point, bias)
     w = q_dequant(w_pack, scale, nbits, group_size, zero_point, x.dtype)
     *leading, _ = x.shape
