@@ -240,3 +240,24 @@ def test_nplinear_constructor_contract():
         NPLinear(blob, torch.rand(16).half(), 8, 64, 32, 4, "sym", "default")  # default needs weight_q
     with pytest.raises(NotImplementedError):
         layer.set_backend("compile")(torch.randn(1, 64))
+
+
+def test_auto_kernel_lowering_config_builds_the_pass():
+    """The serialisable configuration of the lowering pass (reference recipe_config.py:252-286)."""
+    import pydantic
+
+    from neuropress_b200.kernel_lowering import AutoKernelLowering
+    from neuropress_b200.recipe_config import (KERNEL_LOWERING_CONFIG_REGISTRY, AutoKernelLoweringConfig,
+                                               resolve_kernel_lowering_config)
+
+    assert KERNEL_LOWERING_CONFIG_REGISTRY["auto"] is AutoKernelLoweringConfig
+    cfg = resolve_kernel_lowering_config({"type": "auto", "vq_backend": "cuda_lut", "linear_backend": "cuda"})
+    assert cfg.model_dump(mode="json") == {"type": "auto", "linear_backend": "cuda", "vq_backend": "cuda_lut",
+                                           "embedding_backend": "auto", "norm_backend": "auto"}
+    lowering = cfg.build()
+    assert isinstance(lowering, AutoKernelLowering)
+    assert lowering.vq_backend == "cuda_lut" and lowering.linear_backend == "cuda"
+    with pytest.raises(pydantic.ValidationError):
+        AutoKernelLoweringConfig(vq_backend="gemlite")      # not a VQ backend
+    with pytest.raises(ValueError):
+        resolve_kernel_lowering_config({"type": "manual"})
