@@ -275,7 +275,9 @@ __device__ __forceinline__ void q4_emit(const Q4Item<RPL>& it, int n0, int N, ui
 }
 
 // ---- the kernel ------------------------------------------------------------------------------
-template <typename T, int BN, int MT, int BMODE, int BITS>
+// GATHER: the epilogue carries the fused all-gather (dense mode only); a separate instantiation
+// so that the plain kernels do not pay for its registers.
+template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER>
 __global__ void __launch_bounds__(BMODE == B_TMA ? 192 : BMODE == B_VQ ? 320 : 192 + 32 * kQ4DecodeWarps, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p, const int stages) {
@@ -412,7 +414,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // row-wise and copy it to every peer with row-contiguous 16-byte stores -- NVLink carries
     // those far better than the epilogue's own 16-bytes-per-row pattern.  The TMEM buffer is
     // released before the copy, so the next tile's MMAs run under it.
-    const bool gathered = p.sink.peer_out != nullptr;
+    const bool gathered = GATHER && p.sink.peer_out != nullptr;
     const int64_t ld = gathered ? p.sink.ld : p.N;
     const int64_t col0 = gathered ? p.sink.col0 : 0;
     if (gathered) y = static_cast<T*>(p.sink.peer_out[p.sink.rank]);
@@ -496,25 +498,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int cpr = cols / 8;  // 16-byte chunks per row
         const int64_t tile_off = (int64_t)(tm * MT * BM) * ld + col0 + (int64_t)tn * BN;
         const int et = threadIdx.x - 64;  // 0..127 over the epilogue warps
-        constexpr int U = 8;  // 16-byte pieces in flight per thread
+        constexpr int U = 16;  // 16-byte pieces in flight per thread (32 KiB per CTA)
+        auto piece_off = [&](int i) -> int64_t {
+          const int r = i / cpr, c = i - r * cpr;
+          return tile_off + (int64_t)r * ld + c * 8;
+        };
         for (int i0 = et; i0 < rows * cpr; i0 += 128 * U) {
           uint4 vv[U];
-          int64_t offs[U];
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const int i = i0 + u * 128;
-            offs[u] = -1;
-            if (i < rows * cpr) {
-              const int r = i / cpr, c = i - r * cpr;
-              offs[u] = tile_off + (int64_t)r * ld + c * 8;
-              vv[u] = __ldcg(reinterpret_cast<const uint4*>(y + offs[u]));
-            }
+            if (i < rows * cpr) vv[u] = __ldcg(reinterpret_cast<const uint4*>(y + piece_off(i)));
           }
           for (int d = 1; d < p.sink.world; ++d) {
             T* peer = static_cast<T*>(p.sink.peer_out[(p.sink.rank + d) % p.sink.world]);
 #pragma unroll
-            for (int u = 0; u < U; ++u)
-              if (offs[u] >= 0) *reinterpret_cast<uint4*>(peer + offs[u]) = vv[u];
+            for (int u = 0; u < U; ++u) {
+              const int i = i0 + u * 128;
+              if (i < rows * cpr) *reinterpret_cast<uint4*>(peer + piece_off(i)) = vv[u];
+            }
           }
         }
       }
@@ -650,10 +652,10 @@ int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, in
   return NPB_OK;
 }
 
-template <typename T, int BN, int MT, int BMODE, int BITS>
+template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER = false>
 int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t st) {
   constexpr bool bf16 = std::is_same<T, __nv_bfloat16>::value;
-  auto kern = gemm_kernel<T, BN, MT, BMODE, BITS>;
+  auto kern = gemm_kernel<T, BN, MT, BMODE, BITS, GATHER>;
   const int cap = max_dynamic_smem();
   int stages = SmemLayout<BN, MT>::stages(cap);
   if (stages < 2) return NPB_ERR_UNSUPPORTED;
@@ -705,14 +707,14 @@ int pick_bn(int64_t M, int64_t N) {
   return best_bn;
 }
 
-template <typename T>
+template <typename T, bool GATHER>
 int gemm_dense(const void* x, const void* w, GemmParams p, cudaStream_t st) {
   switch (pick_bn(p.M, p.N)) {
-    case 256: return launch_gemm<T, 256, 1, B_TMA, 0>(x, w, p, st);
-    case 224: return launch_gemm<T, 224, 1, B_TMA, 0>(x, w, p, st);
-    case 192: return launch_gemm<T, 192, 1, B_TMA, 0>(x, w, p, st);
-    case 128: return launch_gemm<T, 128, 1, B_TMA, 0>(x, w, p, st);
-    default: return launch_gemm<T, 64, 1, B_TMA, 0>(x, w, p, st);
+    case 256: return launch_gemm<T, 256, 1, B_TMA, 0, GATHER>(x, w, p, st);
+    case 224: return launch_gemm<T, 224, 1, B_TMA, 0, GATHER>(x, w, p, st);
+    case 192: return launch_gemm<T, 192, 1, B_TMA, 0, GATHER>(x, w, p, st);
+    case 128: return launch_gemm<T, 128, 1, B_TMA, 0, GATHER>(x, w, p, st);
+    default: return launch_gemm<T, 64, 1, B_TMA, 0, GATHER>(x, w, p, st);
   }
 }
 
@@ -856,8 +858,13 @@ int gemm_impl(const void* x, const void* w, const float* bias, void* y, int64_t 
   p.bias = bias;
   p.y = y;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  if (sink) p.sink = *sink;
-  return dtype == NPB_BF16 ? gemm_dense<__nv_bfloat16>(x, w, p, st) : gemm_dense<__half>(x, w, p, st);
+  if (sink) {
+    p.sink = *sink;
+    return dtype == NPB_BF16 ? gemm_dense<__nv_bfloat16, true>(x, w, p, st)
+                             : gemm_dense<__half, true>(x, w, p, st);
+  }
+  return dtype == NPB_BF16 ? gemm_dense<__nv_bfloat16, false>(x, w, p, st)
+                           : gemm_dense<__half, false>(x, w, p, st);
 }
 }  // namespace
 
