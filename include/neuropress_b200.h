@@ -162,6 +162,13 @@ int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dt
                                  int64_t N, int64_t K, const float* bias, void* y,
                                  npb_stream_t stream);
 
+/* Fused RMSNorm over the last dimension, the step on the input side of the q/k/v and gate/up
+ * linears: out[m, i] = T(x[m, i] * rsqrt(mean(x[m, :]^2) + eps) * weight[i]), fp32 arithmetic.
+ * Replaces rms_norm (neuropress/kernels/rms_norm.cu:27-123; wrapper kernels/__init__.py:1091-1110).
+ * x, out [M, H] contiguous, weight [H], all of `dtype` (NPB_BF16 / NPB_F16 / NPB_F32). */
+int npb_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_t H, float eps,
+                 int dtype, npb_stream_t stream);
+
 /*
  * Multi-GPU (new; the reference has no distributed code): all-gather of out-feature shards by
  * pushing.  This rank's src[M, n_local] (elem_bytes per element) is stored into columns

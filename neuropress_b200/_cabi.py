@@ -40,6 +40,7 @@ EXPORTED_SYMBOLS = (
     "npb_allgather_push",
     "npb_gemm_allgather",
     "npb_vq_gemv_allgather",
+    "npb_rms_norm",
     "npb_test_vq_decode_tile",
     "npb_gemm_device_status",
 )
@@ -137,6 +138,8 @@ def load_library() -> ctypes.CDLL:
                                        sink_p, c_void_p]
     lib.npb_vq_gemv_allgather.argtypes = [vq_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p,
                                           sink_p, c_void_p]
+    lib.npb_rms_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_float, c_int,
+                                 c_void_p]
     lib.npb_gemm_device_status.argtypes = [POINTER(c_int)]
     for name in EXPORTED_SYMBOLS[3:]:
         getattr(lib, name).restype = c_int

@@ -27,6 +27,7 @@ int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_
                  void*, cudaStream_t);
 
 int gemm_device_status(int*);
+int rms_norm(const void*, const void*, void*, int64_t, int64_t, float, int, cudaStream_t);
 int gemm_gather(const void*, const void*, const float*, int64_t, int64_t, int64_t, int, const GatherSink&,
                 cudaStream_t);
 int vq_gemv_gather(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
@@ -233,6 +234,11 @@ int npb_vq_gemv_allgather(const npb_vq_weight* w, const void* x, int x_dtype, in
   npb::GatherSink s;
   if (int rc = to_sink(sink, &s)) return rc;
   return npb::vq_gemv_gather(w, x, x_dtype, M, N_local, K, bias, s, static_cast<cudaStream_t>(stream));
+}
+
+int npb_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_t H, float eps,
+                 int dtype, npb_stream_t stream) {
+  return npb::rms_norm(x, weight, out, M, H, eps, dtype, static_cast<cudaStream_t>(stream));
 }
 
 int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }

@@ -3,10 +3,10 @@
 Same surface as the reference's ``neuropress/kernel_lowering.py``: :class:`LoweringConfig`
 (:43-116; four string fields, unknown keys rejected, YAML / dict / ``None``),
 :class:`AutoKernelLowering` (:154-249), :func:`is_lowered` (:257-277), :func:`unlower_model`
-(:280-368).  Only the two linear passes exist here — ``linearize_qtensor_weights`` then
-``linearize_vq_weights``, in the reference's order; the embedding and RMSNorm passes of the
-reference are outside this package, so ``embedding_backend`` / ``norm_backend`` are carried in
-the configuration but have no effect.
+(:280-368).  The two linear passes (``linearize_qtensor_weights`` then ``linearize_vq_weights``, in the
+reference's order) and the RMSNorm pass exist here; the embedding pass of the reference is
+outside this package, so ``embedding_backend`` is carried in the configuration but has no
+effect.
 """
 
 from __future__ import annotations
@@ -101,6 +101,12 @@ class AutoKernelLowering(KernelLowering):
 
         linearize_qtensor_weights(model, backend=self.linear_backend)
         linearize_vq_weights(model, backend=self.vq_backend)
+        if self.norm_backend in ("auto", "cuda"):  # "default" keeps the model's own norms
+            from .nn.np_rms_norm import linearize_rms_norms
+
+            n_norms = linearize_rms_norms(model)
+            if n_norms:
+                LOGGER.info("Kernel lowering: %d RMSNorm module(s) fused", n_norms)
         # A lowered lm_head no longer shares storage with the embedding (reference :221-227).
         if hasattr(model, "config") and hasattr(model.config, "tie_word_embeddings"):
             model.config.tie_word_embeddings = False
@@ -147,4 +153,13 @@ def unlower_model(model: nn.Module) -> None:
         setattr(parent, name.rsplit(".", 1)[-1], new_mod)
     for pname in [n for n, _ in model.named_children() if n.startswith("_vq_proxy_")]:
         delattr(model, pname)
+    # fused norms go back to the modules they replaced
+    from .nn.np_rms_norm import NPRMSNorm
+
+    for name, module in list(model.named_modules()):
+        if isinstance(module, NPRMSNorm):
+            source = module.to_source_module()
+            if source is not None:
+                parent = model.get_submodule(name.rsplit(".", 1)[0]) if "." in name else model
+                setattr(parent, name.rsplit(".", 1)[-1], source)
     LOGGER.info("unlower_model: restored %d module(s) to QTensor form", len(replacements))

@@ -350,6 +350,32 @@ def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: 
 
 
 # ---------------------------------------------------------------------------
+# RMSNorm
+# ---------------------------------------------------------------------------
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """Fused single-pass RMSNorm, drop-in for the reference's ``rms_norm``
+    (kernels/__init__.py:1091-1110): ``out[m, i] = x[m, i] * rsqrt(mean(x[m, :]**2) + eps) *
+    weight[i]`` computed in fp32.  ``x`` is ``[M, H]``, ``weight`` ``[H]`` of the same dtype
+    (fp16, bf16 or fp32)."""
+    if x.dim() != 2 or weight.dim() != 1 or weight.shape[0] != x.shape[1]:
+        raise RuntimeError("rms_norm: expected x [M, H] and weight [H].")
+    if x.dtype != weight.dtype:
+        raise RuntimeError("rms_norm: x and weight must share dtype.")
+    _cabi.require_cuda("rms_norm", x, weight)
+    lib = _cabi.load_library()
+    x = x.contiguous()
+    weight = weight.contiguous()
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = _launch("npb_rms_norm", lib.npb_rms_norm, x.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                     x.shape[0], x.shape[1], float(eps), _cabi.dtype_code(x.dtype), _cabi.stream_ptr())
+    _cabi.check(rc, "rms_norm")
+    return out
+
+
+# ---------------------------------------------------------------------------
 # Test hook
 # ---------------------------------------------------------------------------
 

@@ -3,10 +3,11 @@
 from .backends import (Backend, EmbeddingBackend, LinearBackend, NormBackend, VQBackend,
                        is_cuda_jit_available)
 from .np_linear import NPLinear, linearize_qtensor_weights
+from .np_rms_norm import NPRMSNorm, linearize_rms_norms
 from .np_vq_linear import NPVQLinear, VQProxy, linearize_vq_weights
 
 __all__ = [
     "Backend", "EmbeddingBackend", "LinearBackend", "NormBackend", "VQBackend",
     "is_cuda_jit_available", "NPLinear", "linearize_qtensor_weights", "NPVQLinear", "VQProxy",
-    "linearize_vq_weights",
+    "linearize_vq_weights", "NPRMSNorm", "linearize_rms_norms",
 ]

@@ -248,3 +248,26 @@ def rel_max_err(y: torch.Tensor, y_ref: torch.Tensor) -> float:
     r = y_ref.detach().cpu().double()
     rms = float(torch.sqrt(torch.mean(r * r)))
     return float((y - r).abs().max()) / max(rms, 1e-30)
+
+
+# ---------------------------------------------------------------------------
+# RMSNorm (the step on the input side of the lowered linears)
+# ---------------------------------------------------------------------------
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``x * rsqrt(mean(x**2, -1) + eps) * weight`` with fp32 arithmetic and one rounding to the
+    input dtype, as the reference kernel defines it (neuropress/kernels/rms_norm.cu:40-76:
+    fp32 sum of squares, ``rsqrtf(ss / H + eps)``, ``(float)x * scale * (float)weight``) and as
+    its module documents it (neuropress/nn/np_rms_norm.py:45-47).  The reference has no CPU
+    implementation of this kernel; the torch expression of its docstring is the yardstick."""
+    xf = x.to(torch.float32)
+    scale = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (xf * scale * weight.to(torch.float32)).to(x.dtype)
+
+
+def rms_norm_f64(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """The same in float64, unrounded (tolerance checks)."""
+    xd = x.to(torch.float64)
+    scale = torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps)
+    return xd * scale * weight.to(torch.float64)

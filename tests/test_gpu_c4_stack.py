@@ -87,3 +87,12 @@ def test_llama_shaped_stack_matches_dense_weights(bits):
             graph.replay()
             side.synchronize()
         assert _rel_rms(static_out, torch.flip(bq.last_hidden_state, dims=[0])) < 1e-3
+
+        # the norms on the input side of the linears, fused (LlamaRMSNorm: plain-weight convention)
+        from neuropress_b200.nn import NPRMSNorm, linearize_rms_norms
+
+        assert linearize_rms_norms(vq) == 5  # 2 per layer + the final norm
+        assert sum(isinstance(m, NPRMSNorm) for m in vq.modules()) == 5
+        nq = vq(inputs_embeds=prompt, use_cache=False)
+        assert _rel_rms(nq.last_hidden_state, od.last_hidden_state) < 2e-2
+        assert _rel_rms(nq.last_hidden_state, oq.last_hidden_state) < 1e-2

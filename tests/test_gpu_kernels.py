@@ -275,3 +275,26 @@ def test_q_gemm_fused_full_size_layer(asym, gs, rows):
                                None if layer.zero_point is None else layer.zero_point.view(N, -1)[sl].reshape(-1),
                                None)
     assert_output_close(y[:, sl], ref, torch.bfloat16, tol=2e-3)
+
+
+# ------------------------------------------------------------------------- RMSNorm ---
+@pytest.mark.parametrize("shape", [(1, 2048), (5, 8192), (3, 100), (7, 2050), (300, 4096), (2, 16384),
+                                   (4, 33000)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rms_norm_matches_oracle(shape, dtype):
+    """Fused RMSNorm against the fp64 restatement: within one rounding of the output type plus
+    the fp32 error of the sum of squares (rows of every path: cached in registers, re-read,
+    scalar for ragged H)."""
+    M, H = shape
+    g = torch.Generator().manual_seed(M * 7 + H)
+    x = (torch.randn(M, H, generator=g) * 3).to(dtype)
+    w = (torch.rand(H, generator=g) + 0.5).to(dtype)
+    y = kernels.rms_norm(x.to(DEV), w.to(DEV), 1e-5)
+    assert y.dtype == dtype and y.shape == (M, H)
+    ref = oracle.rms_norm_f64(x, w, 1e-5)
+    ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -23}[dtype]
+    err = (y.double().cpu() - ref).abs()
+    assert bool((err <= ref.abs() * (ulp * 1.01 + 1e-5) + 1e-7).all())
+    # and against the fp32 torch expression the reference documents, at most one ulp apart
+    ref32 = oracle.rms_norm(x, w, 1e-5).double()
+    assert bool(((y.double().cpu() - ref32).abs() <= ref32.abs() * ulp * 2.01 + 1e-7).all())

@@ -261,3 +261,51 @@ def test_auto_kernel_lowering_config_builds_the_pass():
         AutoKernelLoweringConfig(vq_backend="gemlite")      # not a VQ backend
     with pytest.raises(ValueError):
         resolve_kernel_lowering_config({"type": "manual"})
+
+
+# ------------------------------------------------------------------------- RMSNorm ---
+class _LlamaStyleRMSNorm(torch.nn.Module):
+    def __init__(self, h, eps=1e-5):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.rand(h) + 0.5)
+        self.eps = eps
+
+    def forward(self, x):
+        v = x.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+
+class _GemmaStyleRMSNorm(_LlamaStyleRMSNorm):
+    def forward(self, x):
+        v = x.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (v * (1.0 + self.weight.float())).to(x.dtype)
+
+
+def test_rms_norm_swap_detects_the_plus_one_convention():
+    """linearize_rms_norms (reference np_rms_norm.py:106-208): detection, the '+1' weight folded
+    in, the source module kept for the way back; the oracle agrees with both source modules."""
+    import oracle
+    from neuropress_b200.kernel_lowering import unlower_model
+    from neuropress_b200.nn.np_rms_norm import NPRMSNorm, linearize_rms_norms
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential()
+    model.add_module("a", _LlamaStyleRMSNorm(48))
+    model.add_module("b", _GemmaStyleRMSNorm(48))
+    model.add_module("c", torch.nn.LayerNorm(48))          # not an RMSNorm: left alone
+    wa, wb = model.a.weight.detach().clone(), model.b.weight.detach().clone()
+    x = torch.randn(5, 48)
+    ya, yb = model.a(x), model.b(x)
+    assert linearize_rms_norms(model, require_cuda=False) == 2
+    assert isinstance(model.a, NPRMSNorm) and isinstance(model.b, NPRMSNorm)
+    assert isinstance(model.c, torch.nn.LayerNorm)
+    assert torch.equal(model.a.weight, wa) and torch.equal(model.b.weight, 1.0 + wb)
+    assert list(model.state_dict()) == ["a.weight", "b.weight", "c.weight", "c.bias"]
+    torch.testing.assert_close(oracle.rms_norm(x, model.a.weight, model.a.eps), ya, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(oracle.rms_norm(x, model.b.weight, model.b.eps), yb, rtol=1e-5, atol=1e-6)
+    with pytest.raises(RuntimeError):
+        model.a(x)                                           # CUDA only: no CPU path
+    unlower_model(model)
+    assert isinstance(model.a, _LlamaStyleRMSNorm) and isinstance(model.b, _GemmaStyleRMSNorm)
+    assert torch.equal(model.b.weight, wb)
