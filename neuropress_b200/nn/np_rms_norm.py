@@ -47,11 +47,21 @@ class NPRMSNorm(nn.Module):
         return f"H={self.weight.shape[0]}, eps={self.eps}"
 
 
+def _eps_of(module: nn.Module) -> float | None:
+    """The epsilon of a source norm.  The reference looks for ``eps`` only
+    (np_rms_norm.py:121-122); HuggingFace's Llama / Mistral / Qwen2 norms call it
+    ``variance_epsilon``, which is accepted here as well."""
+    for attr in ("eps", "variance_epsilon"):
+        if hasattr(module, attr):
+            return float(getattr(module, attr))
+    return None
+
+
 def _is_unfused_rms_norm(module: nn.Module) -> bool:
     if isinstance(module, NPRMSNorm) or "RMSNorm" not in type(module).__name__:
         return False
     params = dict(module.named_parameters(recurse=False))
-    return set(params) == {"weight"} and params["weight"].dim() == 1 and hasattr(module, "eps")
+    return set(params) == {"weight"} and params["weight"].dim() == 1 and _eps_of(module) is not None
 
 
 def _uses_plus_one_convention(module: nn.Module, weight: torch.Tensor) -> bool:
@@ -88,7 +98,7 @@ def linearize_rms_norms(model: nn.Module, require_cuda: bool = True) -> int:
             n_plus_one += 1
         else:
             effective = weight.clone()
-        fused = NPRMSNorm(effective, eps=float(mod.eps), source=mod).to(weight.device, weight.dtype)
+        fused = NPRMSNorm(effective, eps=_eps_of(mod), source=mod).to(weight.device, weight.dtype)
         parent_name, _, attr = name.rpartition(".")
         parent = model.get_submodule(parent_name) if parent_name else model
         setattr(parent, attr, fused)
