@@ -412,7 +412,7 @@ def run_ours(args) -> dict:
     gemv = None
     if gemv_ms:
         gbs = packed_bytes / world / (gemv_ms * 1e-3) / 1e9
-        gemv = {"bound": "hbm", "kernel": "vq_gemv_kernel at 1 row", "achieved": round(gbs, 1),
+        gemv = {"bound": "hbm", "kernel": "npb_vq_gemv at 1 row (vq_gemv_mma_kernel)", "achieved": round(gbs, 1),
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                 "launch_ms": round(gemv_ms, 5)}
 

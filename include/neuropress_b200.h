@@ -43,6 +43,7 @@ typedef enum { NPB_F16 = 0, NPB_BF16 = 1, NPB_F32 = 2 } npb_dtype;
 /* Largest row count the fused GEMV kernels accept (the decode band is 1-2 rows by
  * default; up to this many rows are supported for tuning the band edge). */
 #define NPB_GEMV_MAX_ROWS 8
+#define NPB_VQ_SMALL_BATCH_MAX_ROWS 16 /* npb_vq_gemv, tensor-core form (see there) */
 
 /*
  * One vector-quantized weight matrix W[N, K].
@@ -102,7 +103,11 @@ int npb_q_decode(const npb_q_weight* w, int64_t N, int64_t K, void* out, int out
 /* y[M, N] = x[M, K] . W^T (+ bias), x / y in x_dtype, bias fp32 [N] or NULL.
  * Replaces vq_linear / vq_linear_wmma's GEMV branch / vq_lut_gather
  * (neuropress/kernels/vq_linear.cu:344-424, vq_linear_wmma.cu:187-240,468-540,
- * vq_linear_lut.cu:121-206). */
+ * vq_linear_lut.cu:121-206).  Up to NPB_GEMV_MAX_ROWS rows for every weight form and fp16 /
+ * bf16 / fp32 activations; up to NPB_VQ_SMALL_BATCH_MAX_ROWS rows when the tensor-core kernel
+ * applies (vector_len 8, 8 / 12 / 16-bit indices, K % 1024 == 0, fp16 / bf16 activations,
+ * 8-bit residual indices, codebook groups of a multiple of 256 columns), else
+ * NPB_ERR_UNSUPPORTED for more than NPB_GEMV_MAX_ROWS rows. */
 int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
                 int64_t K, const float* bias, void* y, npb_stream_t stream);
 

@@ -31,7 +31,7 @@ SOURCES = [
     "q_gemv_mma.cu",
     "gemm_tcgen05.cu",
     "static_scratch.cu",
-    "allgather_push.cu", "rms_norm.cu",
+    "allgather_push.cu", "rms_norm.cu", "vq_gemv_mma.cu",
 ]
 
 NVCC_FLAGS = [

@@ -27,6 +27,8 @@ int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_
                  void*, cudaStream_t);
 
 int gemm_device_status(int*);
+int vq_gemv_mma(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
+                cudaStream_t);
 int rms_norm(const void*, const void*, void*, int64_t, int64_t, float, int, cudaStream_t);
 int gemm_gather(const void*, const void*, const float*, int64_t, int64_t, int64_t, int, const GatherSink&,
                 cudaStream_t);
@@ -166,6 +168,12 @@ int npb_q_decode(const npb_q_weight* w, int64_t N, int64_t K, void* out, int out
 
 int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
                 int64_t K, const float* bias, void* y, npb_stream_t stream) {
+  // The tensor-core kernel where the weight form allows it (it is as fast at 16 rows as the
+  // CUDA-core GEMV at one); else the CUDA-core GEMV, which takes up to NPB_GEMV_MAX_ROWS rows.
+  if (M >= 1 && M <= NPB_VQ_SMALL_BATCH_MAX_ROWS && N > 0) {
+    const int rc = npb::vq_gemv_mma(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+    if (rc != NPB_ERR_UNSUPPORTED) return rc;
+  }
   return npb::vq_gemv(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
 }
 

@@ -1,0 +1,297 @@
+// Fused index-decode linear for 1..16 activation rows on the tensor cores (mma.sync):
+//
+//   y[m, n] = sum_k x[m, k] * W[n, k] + bias[n],   W decoded on the fly exactly as the one-pass
+//   decode produces it (fp16 add of the residual, fp16 multiply by the row scale, one rounding
+//   to the activation type), never written to memory.
+//
+// The weight is the A operand of mma.m16n8k16 (16 output rows x 16 k), the activations the B
+// operand (16 k x 8 activation rows; two B tiles for 9..16 rows), so one decoded 16-row slab is
+// used by every activation row.  Because a sum over k does not care about the order of its
+// terms, the k slots of an mma need not be consecutive k: lane (g, t) of a warp (g = lane / 4,
+// t = lane % 4) owns whole centroid vectors -- for its rows g and g + 8, vectors 8 t + s of the
+// warp's 32-vector K slice, s = 0..7 -- and feeds elements 0..3 of a vector to one mma and 4..7
+// to the next, while the B operand supplies the activations of exactly those k (one 16-byte
+// shared-memory load per lane, XOR-swizzled so that it is conflict-free).  So every gather is a
+// full 16-byte centroid, every index load a 16-byte (8 x 16-bit) run, as in the GEMV.
+//
+// CTA = W warps, warp w owns K slice(s) w (256 k each); a CTA walks 16-row groups of W (strided
+// by the grid); per group the warps' partial 16 x 16 tiles are summed through shared memory
+// (double-buffered, one __syncthreads per group).  Bound by the same centroid-gather rate as
+// the GEMV, but independent of the row count up to 16.
+//
+// Stands in for the GEMM branch of vq_linear_wmma at small batches
+// (neuropress/kernels/vq_linear_wmma.cu:261-394) and for _vq_gemv above 2 rows (:187-240).
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace npb {
+namespace {
+
+struct MmaVqArgs {
+  const uint8_t* packed;
+  const __half* centroids;
+  const uint8_t* res_packed;   // never null: aliases `packed` when there is no residual
+  const __half* res_centroids; // never null: aliases `centroids`
+  const __half* row_scale;     // never null: aliases `centroids`
+  const float* bias;
+  const void* x;
+  void* y;
+  int has_res, has_scale;
+  int num_centroids, res_num_centroids, groups_per_codebook;
+  int M, N, K, G;
+  int slices_per_warp;
+};
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+// fp16 pair -> the activation type, one rounding (bf16 through fp32, as from_half<bf16>).
+template <typename T>
+__device__ __forceinline__ uint32_t to_operand(__half2 h) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const float2 f = __half22float2(h);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+    return *reinterpret_cast<const uint32_t*>(&b);
+  } else {
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+}
+
+// Physical 16-byte chunk of logical chunk c (= vector index inside the K slice) in a row of
+// the activation tile: lanes t = 0..3 of a quad read chunks 8 t + s, which this spreads over
+// four different bank groups.
+__device__ __forceinline__ int xchunk(int c) { return c ^ ((c >> 3) & 3); }
+
+template <typename T, int BITS, int MT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int K = a.K;
+  // x tile: [MT * 8 rows][K] of T, row stride K * 2 + 64 bytes (rows g and g + 1 of a quarter-warp
+  // pass then fall into different halves of the banks); chunks swizzled per 32-vector slice.
+  const int xstride = K * (int)sizeof(T) + 64;
+  uint8_t* xs = smem;
+  float* part = reinterpret_cast<float*>(smem + (size_t)MT * 8 * xstride);  // [2][WARPS][MT][32][4]
+  uint4* rtab = reinterpret_cast<uint4*>(part + 2 * WARPS * MT * 128);      // residual table x 8
+
+  // ---- stage activations (zero rows past M) and the replicated residual table ----
+  {
+    const T* x = static_cast<const T*>(a.x);
+    const int chunks = K / 8;
+    for (int i = tid; i < MT * 8 * chunks; i += WARPS * 32) {
+      const int m = i / chunks, c = i - m * chunks;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m < a.M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + c * 8);
+      const int phys = (c & ~31) | xchunk(c & 31);
+      *reinterpret_cast<uint4*>(xs + (size_t)m * xstride + phys * 16) = v;
+    }
+    if (a.has_res) {
+      // entry e at slots 8 e .. 8 e + 7; a lane reads slot 8 e + (lane & 7): conflict-free
+      for (int i = tid; i < a.res_num_centroids * 8; i += WARPS * 32)
+        rtab[i] = __ldg(reinterpret_cast<const uint4*>(a.res_centroids) + (i >> 3));
+    }
+  }
+  __syncthreads();
+
+  const int n_groups = (a.N + 15) / 16;
+  const int chunks_per_row = a.G >> 3;  // 8-index chunks per W row
+  const bool has_res = a.has_res != 0, has_scale = a.has_scale != 0;
+  int buf = 0;
+  for (int rg = blockIdx.x; rg < n_groups; rg += gridDim.x, buf ^= 1) {
+    const int n_lo = rg * 16 + g, n_hi = n_lo + 8;
+    // rows past N read row N - 1 (mapped); their results are not stored
+    const int r_lo = n_lo < a.N ? n_lo : a.N - 1, r_hi = n_hi < a.N ? n_hi : a.N - 1;
+    __half2 s_lo = __float2half2_rn(1.f), s_hi = s_lo;
+    if (has_scale) {
+      s_lo = __half2half2(__ldg(a.row_scale + (has_scale ? r_lo : 0)));
+      s_hi = __half2half2(__ldg(a.row_scale + (has_scale ? r_hi : 0)));
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+
+    for (int sl = 0; sl < a.slices_per_warp; ++sl) {
+      const int slice = warp * a.slices_per_warp + sl;  // 32 vectors = 256 k
+      const int v0 = slice * 32 + 8 * t;                // this lane's 8 vectors of the slice
+      uint32_t idx_lo[8], idx_hi[8], rdx_lo[8], rdx_hi[8];
+      read_index8<BITS>(a.packed, (int64_t)r_lo * chunks_per_row + (v0 >> 3), idx_lo);
+      read_index8<BITS>(a.packed, (int64_t)r_hi * chunks_per_row + (v0 >> 3), idx_hi);
+#pragma unroll
+      for (int s = 0; s < 8; ++s) { rdx_lo[s] = 0; rdx_hi[s] = 0; }
+      if (has_res) {
+        read_index8<8>(a.res_packed, (int64_t)r_lo * chunks_per_row + (v0 >> 3), rdx_lo);
+        read_index8<8>(a.res_packed, (int64_t)r_hi * chunks_per_row + (v0 >> 3), rdx_hi);
+      }
+      if (a.groups_per_codebook > 0) {  // a multiple of 32 vectors: constant over the slice
+        const uint32_t off = (uint32_t)((slice * 32) / a.groups_per_codebook) * (uint32_t)a.num_centroids;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) { idx_lo[s] += off; idx_hi[s] += off; }
+      }
+      const uint8_t* xrow = xs + (size_t)g * xstride + (size_t)slice * 512;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {  // two batches of four vectors per row: 8 gathers in flight
+        Half8 c_lo[4], c_hi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(a.centroids) + idx_lo[4 * h + j]);
+          c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(a.centroids) + idx_hi[4 * h + j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int s = 4 * h + j;
+          __half2 w_lo[4], w_hi[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { w_lo[i] = c_lo[j].h[i]; w_hi[i] = c_hi[j].h[i]; }
+          if (has_res) {
+            const Half8 q_lo = *reinterpret_cast<const Half8*>(&rtab[(rdx_lo[s] << 3) + (lane & 7)]);
+            const Half8 q_hi = *reinterpret_cast<const Half8*>(&rtab[(rdx_hi[s] << 3) + (lane & 7)]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              w_lo[i] = __hadd2_rn(w_lo[i], q_lo.h[i]);
+              w_hi[i] = __hadd2_rn(w_hi[i], q_hi.h[i]);
+            }
+          }
+          if (has_scale) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              w_lo[i] = __hmul2_rn(w_lo[i], s_lo);
+              w_hi[i] = __hmul2_rn(w_hi[i], s_hi);
+            }
+          }
+          // elements 0..3 of the two vectors -> first mma, 4..7 -> second
+          const uint32_t a0[4] = {to_operand<T>(w_lo[0]), to_operand<T>(w_hi[0]), to_operand<T>(w_lo[1]),
+                                  to_operand<T>(w_hi[1])};
+          const uint32_t a1[4] = {to_operand<T>(w_lo[2]), to_operand<T>(w_hi[2]), to_operand<T>(w_lo[3]),
+                                  to_operand<T>(w_hi[3])};
+          const int phys = xchunk(8 * t + s);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xrow + (size_t)mt * 8 * xstride + phys * 16);
+            mma16816<T>(acc[mt], a0, xv.x, xv.y);
+            mma16816<T>(acc[mt], a1, xv.z, xv.w);
+          }
+        }
+      }
+    }
+
+    // ---- sum the warps' partial tiles and store ----
+    float* mine = part + ((size_t)buf * WARPS + warp) * MT * 128;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+      *reinterpret_cast<float4*>(mine + mt * 128 + lane * 4) =
+          make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
+    __syncthreads();
+    for (int i = tid; i < MT * 128; i += WARPS * 32) {  // a 4-warp CTA has fewer threads than outputs
+      float sum = 0.f;
+      const float* p = part + (size_t)buf * WARPS * MT * 128 + i;
+#pragma unroll 4
+      for (int w = 0; w < WARPS; ++w) sum += p[(size_t)w * MT * 128];
+      const int mt = i >> 7, ln = (i >> 2) & 31, c = i & 3;
+      const int n = rg * 16 + (ln >> 2) + 8 * (c >> 1);
+      const int m = mt * 8 + 2 * (ln & 3) + (c & 1);
+      if (n < a.N && m < a.M) {
+        if (a.bias) sum += __ldg(a.bias + n);
+        static_cast<T*>(a.y)[(size_t)m * a.N + n] = from_f32<T>(sum);
+      }
+    }
+    // No second barrier: the next group writes the other half of `part`, and the barrier of
+    // that group orders this group's reads before the writes of the group after it.
+  }
+}
+
+template <typename T, int BITS, int MT, int WARPS>
+int launch(const MmaVqArgs& a, cudaStream_t st) {
+  const size_t xbytes = (size_t)MT * 8 * ((size_t)a.K * sizeof(T) + 64);
+  const size_t smem = xbytes + (size_t)2 * WARPS * MT * 128 * 4 + (a.has_res ? 256 * 8 * 16 : 0);
+  if (smem > (size_t)max_dynamic_smem()) return NPB_ERR_UNSUPPORTED;
+  auto kern = vq_gemv_mma_kernel<T, BITS, MT, WARPS>;
+  int per_sm = 0;
+  if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), WARPS * 32, smem, &per_sm)) return rc;
+  if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
+  const int n_groups = (a.N + 15) / 16;
+  const int cap = sm_count() * per_sm;
+  kern<<<n_groups < cap ? n_groups : cap, WARPS * 32, smem, st>>>(a);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+template <typename T, int BITS, int MT>
+int launch_warps(MmaVqArgs a, cudaStream_t st) {
+  const int slices = a.K / 256;
+  if (slices % 16 == 0) { a.slices_per_warp = slices / 16; return launch<T, BITS, MT, 16>(a, st); }
+  if (slices % 8 == 0) { a.slices_per_warp = slices / 8; return launch<T, BITS, MT, 8>(a, st); }
+  if (slices % 4 == 0) { a.slices_per_warp = slices / 4; return launch<T, BITS, MT, 4>(a, st); }
+  return NPB_ERR_UNSUPPORTED;
+}
+
+template <typename T, int BITS>
+int launch_mt(const MmaVqArgs& a, cudaStream_t st) {
+  return a.M <= 8 ? launch_warps<T, BITS, 1>(a, st) : launch_warps<T, BITS, 2>(a, st);
+}
+
+template <typename T>
+int launch_bits(const MmaVqArgs& a, int bits, cudaStream_t st) {
+  switch (bits) {
+    case 16: return launch_mt<T, 16>(a, st);
+    case 12: return launch_mt<T, 12>(a, st);
+    case 8: return launch_mt<T, 8>(a, st);
+    default: return NPB_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+
+// Returns NPB_ERR_UNSUPPORTED when the weight form / shape is not one this kernel takes; the
+// caller then uses the CUDA-core GEMV (up to 8 rows) or decode + dense GEMM.
+int vq_gemv_mma(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                const float* bias, void* y, cudaStream_t st) {
+  if (int rc = validate_vq(w, N, K)) return rc;
+  if (x_dtype != NPB_BF16 && x_dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
+  if (M < 1 || M > 16 || N < 1 || N >= (int64_t)1 << 31 || K % 1024 != 0 || K > 16384) return NPB_ERR_UNSUPPORTED;
+  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (w->vector_len != 8 || (w->bits != 16 && w->bits != 12 && w->bits != 8)) return NPB_ERR_UNSUPPORTED;
+  if (!aligned_to(w->packed, index8_alignment(w->bits)) || !aligned_to(w->centroids, 16) || !aligned_to(x, 16))
+    return NPB_ERR_UNSUPPORTED;
+  if (w->res_packed && (w->res_bits != 8 || w->res_num_centroids > 256 || !aligned_to(w->res_packed, 8) ||
+                        !aligned_to(w->res_centroids, 16)))
+    return NPB_ERR_UNSUPPORTED;
+  const int gpc = w->cols_per_codebook > 0 ? w->cols_per_codebook / 8 : 0;
+  if (gpc % 32 != 0) return NPB_ERR_UNSUPPORTED;
+  MmaVqArgs a{};
+  a.packed = w->packed;
+  a.centroids = static_cast<const __half*>(w->centroids);
+  a.has_res = w->res_packed != nullptr;
+  a.has_scale = w->row_scale != nullptr;
+  a.res_packed = a.has_res ? w->res_packed : w->packed;
+  a.res_centroids = a.has_res ? static_cast<const __half*>(w->res_centroids) : a.centroids;
+  a.row_scale = a.has_scale ? static_cast<const __half*>(w->row_scale) : a.centroids;
+  a.bias = bias;
+  a.x = x;
+  a.y = y;
+  a.num_centroids = w->num_centroids;
+  a.res_num_centroids = a.has_res ? w->res_num_centroids : 0;
+  a.groups_per_codebook = gpc;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.G = (int)(K / 8);
+  return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(a, w->bits, st)
+                             : launch_bits<__half>(a, w->bits, st);
+}
+
+}  // namespace npb

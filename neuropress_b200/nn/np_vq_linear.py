@@ -50,6 +50,11 @@ _FUSED_MAX_TOKENS: int = int(os.environ.get("NEUROPRESS_VQ_FUSED_MAX_TOKENS", "2
 _LUT_MAX_TOKENS: int = int(os.environ.get("NEUROPRESS_VQ_LUT_MAX_TOKENS", "2"))
 _TRITON_MAX_TOKENS: int = int(os.environ.get("NEUROPRESS_VQ_TRITON_MAX_TOKENS", "384"))
 
+# Not in the reference: between the GEMV band and the tile-decode band, batches up to this many
+# rows run the tensor-core small-batch kernel (decode in registers, mma.sync) where the weight
+# form allows it (see NPVQLinear._small_batch_ok); 0 switches the band off.
+_SMALL_BATCH_MAX_TOKENS: int = int(os.environ.get("NEUROPRESS_B200_VQ_SMALL_BATCH_MAX_TOKENS", "16"))
+
 # cuda_lut layers take the tile-decode band too (the reference skips it for them).
 _LUT_SKIPS_TILE_BAND: bool = False
 
@@ -295,6 +300,8 @@ class NPVQLinear(nn.Module):
         if self.backend in _FUSED_BACKENDS:
             m = x.numel() // self.in_features
             if m > _fused_max_tokens(self.backend):
+                if m <= _SMALL_BATCH_MAX_TOKENS and self._small_batch_ok(x, m):
+                    return self._forward_gemv(x, gather)
                 skip_tile = _LUT_SKIPS_TILE_BAND and self.backend == VQBackend.CUDA_LUT
                 if not skip_tile and m <= _TRITON_MAX_TOKENS:
                     return self._forward_triton(x, gather)
@@ -342,12 +349,28 @@ class NPVQLinear(nn.Module):
         *leading, _ = x.shape
         return x.reshape(-1, self.in_features).contiguous(), leading
 
+    def _small_batch_ok(self, x: torch.Tensor, m: int) -> bool:
+        """Whether ``npb_vq_gemv`` takes *m* (3..16) rows of *x* on its tensor-core path: the
+        conditions of ``vq_gemv_mma`` (csrc/vq_gemv_mma.cu) plus its shared-memory budget."""
+        k = self.in_features
+        if x.dtype not in (torch.bfloat16, torch.float16) or self.vector_len != 8:
+            return False
+        if self.bits not in (8, 12, 16) or k % 1024 or k > (4096 if m > 8 else 8192):
+            return False
+        if self.cols_per_codebook and self.cols_per_codebook % 256:
+            return False
+        if self.residual_indices is not None and (self.residual_bits != 8
+                                                  or self.residual_proxy.num_centroids > 256):
+            return False
+        return True
+
     # -- band (a): fused index-decode GEMV
     def _forward_gemv(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         from .. import kernels
 
         x2, leading = self._flat(x)
-        fused = gather is not None and gather.accepts(x2.shape[0], x2.dtype)
+        # the GEMV with the all-gather in its tail takes up to 8 rows
+        fused = gather is not None and x2.shape[0] <= 8 and gather.accepts(x2.shape[0], x2.dtype)
         y = kernels.vq_gemv(x2, self.packed_indices, self.proxy.centroids, self.bits,
                             self.out_features, self._bias32(), gather=gather if fused else None,
                             **self._ext())

@@ -122,6 +122,31 @@ def test_vq_gemv_matches_oracle(case, dtype, rows):
     assert_output_close(y, _vq_forward_ref64(layer, x), dtype)
 
 
+SMALL_BATCH_CASES = [
+    # (N, K, NC, bits, residual, scale, cols_per_codebook, bias): forms the tensor-core kernel takes
+    (2048, 2048, 256, 8, 0, False, 0, False),
+    (300, 1024, 4096, 12, 0, False, 0, True),
+    (300, 1024, 4096, 16, 0, False, 512, False),
+    (257, 2048, 65536, 16, 256, True, 0, True),
+    (130, 4096, 4096, 16, 16, True, 2048, False),      # 16-entry residual table, two codebooks
+]
+
+
+@pytest.mark.parametrize("case", SMALL_BATCH_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows", [3, 9, 16])
+def test_vq_small_batch_tensor_core_kernel_matches_oracle(case, dtype, rows):
+    """3..16 rows through npb_vq_gemv: decode in registers + mma.sync (vq_gemv_mma.cu)."""
+    N, K, NC, bits, res, scale, cpc, bias = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K, residual_centroids=res,
+                          row_scale=scale, cols_per_codebook=cpc, bias=bias)
+    x = make_activations(rows, K, dtype, seed=rows)
+    y = kernels.vq_gemv(x.to(DEV), layer.packed.to(DEV), layer.centroids.to(DEV), bits, N,
+                        None if layer.bias is None else layer.bias.to(DEV), **_vq_ext_gpu(layer))
+    assert y.shape == (rows, N) and y.dtype == dtype
+    assert_output_close(y, _vq_forward_ref64(layer, x), dtype)
+
+
 def test_vq_gemv_rejects_too_many_rows():
     layer = make_vq_layer(16, 64, num_centroids=16, seed=1)
     x = make_activations(9, 64, torch.float16).to(DEV)
