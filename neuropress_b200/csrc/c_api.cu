@@ -77,6 +77,9 @@ int max_dynamic_smem() {
 int blocks_per_sm(const void* kernel, int threads, size_t smem, int* per_sm) {
   static std::mutex mu;
   static std::map<std::tuple<int, const void*, size_t>, int> cache;
+  // Largest dynamic shared-memory size opted into so far, per device and kernel: the attribute
+  // is a maximum, so it is only ever raised (lowering it would break a later, larger launch).
+  static std::map<std::pair<int, const void*>, size_t> opted;
   int dev = 0;
   NPB_CUDA_TRY(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> lock(mu);
@@ -84,8 +87,11 @@ int blocks_per_sm(const void* kernel, int threads, size_t smem, int* per_sm) {
   auto it = cache.find(key);
   if (it == cache.end()) {
     // opt in as soon as dynamic + (small) static shared memory can pass the 48 KiB default
-    if (smem + 1024 > 48 * 1024)
+    size_t& have = opted[std::make_pair(dev, kernel)];
+    if (smem + 1024 > 48 * 1024 && smem > have) {
       NPB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      have = smem;
+    }
     int n = 0;
     NPB_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem));
     it = cache.emplace(key, n).first;

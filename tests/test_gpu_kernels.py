@@ -128,7 +128,7 @@ SMALL_BATCH_CASES = [
     (300, 1024, 4096, 12, 0, False, 0, True),
     (300, 1024, 4096, 16, 0, False, 512, False),
     (257, 2048, 65536, 16, 256, True, 0, True),
-    (130, 4096, 4096, 16, 16, True, 2048, False),      # 16-entry residual table, two codebooks
+    (130, 4096, 4096, 16, 256, True, 2048, False),     # two codebooks of 2048 columns + residual
 ]
 
 
