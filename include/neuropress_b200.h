@@ -197,7 +197,8 @@ int npb_allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem
  * from the GEMM epilogue / the GEMV's final store) and ends with the handshake of
  * npb_allgather_push, so no separate gather pass runs.  Same flag words, epochs and rules as
  * npb_allgather_push; all buffers 16-byte aligned, ld and col0 in elements of the activation
- * dtype.  Every rank must make the call (M > 0).  npb_vq_gemv_allgather takes M <= 8 rows.
+ * dtype.  Every rank must make the call (M > 0).  npb_vq_gemv_allgather takes the row counts
+ * of npb_vq_gemv.
  */
 typedef struct npb_gather_sink {
   const void* peer_out;    /* device array [world] of buffer base pointers */

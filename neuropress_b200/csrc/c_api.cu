@@ -28,7 +28,7 @@ int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_
 
 int gemm_device_status(int*);
 int vq_gemv_mma(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
-                cudaStream_t);
+                const GatherSink*, cudaStream_t);
 int rms_norm(const void*, const void*, void*, int64_t, int64_t, float, int, cudaStream_t);
 int gemm_gather(const void*, const void*, const float*, int64_t, int64_t, int64_t, int, const GatherSink&,
                 cudaStream_t);
@@ -177,7 +177,7 @@ int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, i
   // The tensor-core kernel where the weight form allows it (it is as fast at 16 rows as the
   // CUDA-core GEMV at one); else the CUDA-core GEMV, which takes up to NPB_GEMV_MAX_ROWS rows.
   if (M >= 1 && M <= NPB_VQ_SMALL_BATCH_MAX_ROWS && N > 0) {
-    const int rc = npb::vq_gemv_mma(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+    const int rc = npb::vq_gemv_mma(w, x, x_dtype, M, N, K, bias, y, nullptr, static_cast<cudaStream_t>(stream));
     if (rc != NPB_ERR_UNSUPPORTED) return rc;
   }
   return npb::vq_gemv(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));

@@ -70,4 +70,36 @@ __device__ __forceinline__ void gather_signal_and_wait(const GatherSink& g, int 
   __syncwarp();
 }
 
+// Tail of a kernel whose CTAs have written this rank's [M, n_cols] result (a few KiB: the GEMV
+// and small-batch kernels) into the rank's OWN buffer: every thread of every CTA calls it once
+// its stores are issued.  The last CTA to arrive copies the slice to every peer with
+// row-contiguous 16-byte stores and runs the handshake.  n_cols * sizeof(T), ld * sizeof(T) and
+// col0 * sizeof(T) must be multiples of 16.
+template <typename T>
+__device__ __forceinline__ void gather_tail_small(const GatherSink& g, int M, int n_cols) {
+  __shared__ int is_last;
+  const int tid = threadIdx.x;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = gather_cta_arrive(g, gridDim.x) ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const T* mine = static_cast<const T*>(g.peer_out[g.rank]);
+  constexpr int EPC = 16 / (int)sizeof(T);  // elements per 16-byte chunk
+  const int cpr = n_cols / EPC;
+  for (int i = tid; i < M * cpr; i += blockDim.x) {
+    const int m = i / cpr, c = i - m * cpr;
+    const size_t off = (size_t)m * g.ld + g.col0 + (size_t)c * EPC;
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine + off));
+    for (int d = 1; d < g.world; ++d) {
+      T* peer = static_cast<T*>(g.peer_out[(g.rank + d) % g.world]);
+      *reinterpret_cast<uint4*>(peer + off) = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < 32) gather_signal_and_wait(g, tid);
+}
+
 }  // namespace npb

@@ -225,32 +225,7 @@ __global__ void __launch_bounds__(kThreads) vq_gemv_kernel(GemvArgs a) {
       }
     }
   }
-  if (a.sink.peer_out != nullptr) {
-    // The last CTA to finish copies the whole [M, N] slice (a few KiB) to every peer with
-    // row-contiguous 16-byte stores, then runs the handshake.
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) is_last = gather_cta_arrive(a.sink, gridDim.x) ? 1 : 0;
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    const T* mine = static_cast<const T*>(a.sink.peer_out[a.sink.rank]);
-    constexpr int EPC = 16 / (int)sizeof(T);  // elements per 16-byte chunk
-    const int cpr = a.N / EPC;
-    for (int i = tid; i < a.M * cpr; i += kThreads) {
-      const int m = i / cpr, c = i - m * cpr;
-      const size_t off = (size_t)m * a.sink.ld + a.sink.col0 + (size_t)c * EPC;
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(mine + off));
-      for (int d = 1; d < a.sink.world; ++d) {
-        T* peer = static_cast<T*>(a.sink.peer_out[(a.sink.rank + d) % a.sink.world]);
-        *reinterpret_cast<uint4*>(peer + off) = v;
-      }
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (warp == 0) gather_signal_and_wait(a.sink, lane);
-  }
+  if (a.sink.peer_out != nullptr) gather_tail_small<T>(a.sink, a.M, a.N);
 }
 
 template <typename T, int VL, int BITS, int MT, bool CB_SMEM>
@@ -344,6 +319,8 @@ int run(const npb_vq_weight* w, GemvArgs a, cudaStream_t st) {
 
 }  // namespace
 
+int vq_gemv_mma(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
+                const GatherSink*, cudaStream_t);
 namespace {
 int vq_gemv_impl(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
                  const float* bias, void* y, const GatherSink* sink, cudaStream_t st);
@@ -366,6 +343,10 @@ int vq_gemv_gather(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M
   if (M <= 0 || N <= 0) return NPB_ERR_INVALID_ARG;  // every rank must run the handshake
   const int64_t epc = x_dtype == NPB_F32 ? 4 : 8;    // elements per 16-byte piece of a row
   if (N % epc != 0 || sink.ld % epc != 0 || sink.col0 % epc != 0) return NPB_ERR_ALIGNMENT;
+  if (M <= NPB_VQ_SMALL_BATCH_MAX_ROWS) {  // tensor-core kernel where the weight form allows it
+    const int rc = vq_gemv_mma(w, x, x_dtype, M, N, K, bias, nullptr, &sink, st);
+    if (rc != NPB_ERR_UNSUPPORTED) return rc;
+  }
   return vq_gemv_impl(w, x, x_dtype, M, N, K, bias, nullptr, &sink, st);
 }
 

@@ -24,6 +24,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "gather_sink.cuh"
 
 namespace npb {
 namespace {
@@ -41,6 +42,7 @@ struct MmaVqArgs {
   int num_centroids, res_num_centroids, groups_per_codebook;
   int M, N, K, G;
   int slices_per_warp;
+  GatherSink sink;  // peer_out != null: y goes to this rank's own [M, ld] buffer, then the tail
 };
 
 template <typename T>
@@ -209,12 +211,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
       const int m = mt * 8 + 2 * (ln & 3) + (c & 1);
       if (n < a.N && m < a.M) {
         if (a.bias) sum += __ldg(a.bias + n);
-        static_cast<T*>(a.y)[(size_t)m * a.N + n] = from_f32<T>(sum);
+        if (a.sink.peer_out == nullptr)
+          static_cast<T*>(a.y)[(size_t)m * a.N + n] = from_f32<T>(sum);
+        else
+          static_cast<T*>(a.sink.peer_out[a.sink.rank])[(size_t)m * a.sink.ld + a.sink.col0 + n] =
+              from_f32<T>(sum);
       }
     }
     // No second barrier: the next group writes the other half of `part`, and the barrier of
     // that group orders this group's reads before the writes of the group after it.
   }
+  if (a.sink.peer_out != nullptr) gather_tail_small<T>(a.sink, a.M, a.N);
 }
 
 template <typename T, int BITS, int MT, int WARPS>
@@ -262,11 +269,11 @@ int launch_bits(const MmaVqArgs& a, int bits, cudaStream_t st) {
 // Returns NPB_ERR_UNSUPPORTED when the weight form / shape is not one this kernel takes; the
 // caller then uses the CUDA-core GEMV (up to 8 rows) or decode + dense GEMM.
 int vq_gemv_mma(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
-                const float* bias, void* y, cudaStream_t st) {
+                const float* bias, void* y, const GatherSink* sink, cudaStream_t st) {
   if (int rc = validate_vq(w, N, K)) return rc;
   if (x_dtype != NPB_BF16 && x_dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
   if (M < 1 || M > 16 || N < 1 || N >= (int64_t)1 << 31 || K % 1024 != 0 || K > 16384) return NPB_ERR_UNSUPPORTED;
-  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (x == nullptr || (y == nullptr && sink == nullptr)) return NPB_ERR_INVALID_ARG;
   if (w->vector_len != 8 || (w->bits != 16 && w->bits != 12 && w->bits != 8)) return NPB_ERR_UNSUPPORTED;
   if (!aligned_to(w->packed, index8_alignment(w->bits)) || !aligned_to(w->centroids, 16) || !aligned_to(x, 16))
     return NPB_ERR_UNSUPPORTED;
@@ -290,6 +297,7 @@ int vq_gemv_mma(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, i
   a.res_num_centroids = a.has_res ? w->res_num_centroids : 0;
   a.groups_per_codebook = gpc;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.G = (int)(K / 8);
+  if (sink) a.sink = *sink;
   return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(a, w->bits, st)
                              : launch_bits<__half>(a, w->bits, st);
 }

@@ -369,8 +369,7 @@ class NPVQLinear(nn.Module):
         from .. import kernels
 
         x2, leading = self._flat(x)
-        # the GEMV with the all-gather in its tail takes up to 8 rows
-        fused = gather is not None and x2.shape[0] <= 8 and gather.accepts(x2.shape[0], x2.dtype)
+        fused = gather is not None and gather.accepts(x2.shape[0], x2.dtype)
         y = kernels.vq_gemv(x2, self.packed_indices, self.proxy.centroids, self.bits,
                             self.out_features, self._bias32(), gather=gather if fused else None,
                             **self._ext())
