@@ -309,3 +309,32 @@ def test_rms_norm_swap_detects_the_plus_one_convention():
     unlower_model(model)
     assert isinstance(model.a, _LlamaStyleRMSNorm) and isinstance(model.b, _GemmaStyleRMSNorm)
     assert torch.equal(model.b.weight, wb)
+
+
+def test_small_batch_band_sits_between_the_gemv_and_the_tile_band(monkeypatch):
+    """3..16 rows go to the fused kernel when the weight form fits the tensor-core small-batch
+    kernel (vector length 8, 8/12/16-bit indices, K % 1024 == 0, fp16/bf16), else on to the
+    tile-decode band as in the reference."""
+    from neuropress_b200.synthetic import make_vq_layer
+
+    d = make_vq_layer(32, 1024, num_centroids=256, bits=8, seed=3)
+    layer = NPVQLinear(VQProxy(d.centroids), d.packed, 8, 32, 1024, 8, backend="cuda_wmma")
+    calls = []
+    monkeypatch.setattr(layer, "_forward_cuda_wmma", lambda x, gather=None: calls.append("gemv") or x[..., :32])
+    monkeypatch.setattr(layer, "_forward_gemv", lambda x, gather=None: calls.append("small") or x[..., :32])
+    monkeypatch.setattr(layer, "_forward_triton", lambda x, gather=None: calls.append("tile") or x[..., :32])
+    monkeypatch.setattr(layer, "_forward_dequant_gemm", lambda x, gather=None: calls.append("dense") or x[..., :32])
+    layer(torch.zeros(2, 1024, dtype=torch.bfloat16))      # reference GEMV band
+    layer(torch.zeros(3, 1024, dtype=torch.bfloat16))      # small-batch band
+    layer(torch.zeros(16, 1024, dtype=torch.bfloat16))     # ... up to 16 rows
+    layer(torch.zeros(17, 1024, dtype=torch.bfloat16))     # tile-decode band
+    layer(torch.zeros(16, 1024, dtype=torch.float32))      # fp32 activations: not the tensor-core form
+    assert calls == ["gemv", "small", "small", "tile", "tile"]
+    assert layer._small_batch_ok(torch.zeros(1, 1024, dtype=torch.float16), 9)
+    assert not layer._small_batch_ok(torch.zeros(1, 1024, dtype=torch.float32), 9)
+    wide = NPVQLinear(VQProxy(d.centroids), d.packed[: 4 * 1024], 8, 4, 8192, 8, backend="cuda_wmma")
+    assert wide._small_batch_ok(torch.zeros(1, 8192, dtype=torch.bfloat16), 8)
+    assert not wide._small_batch_ok(torch.zeros(1, 8192, dtype=torch.bfloat16), 9)   # two B tiles do not fit
+    monkeypatch.setattr(vqmod, "_SMALL_BATCH_MAX_TOKENS", 0)
+    layer(torch.zeros(3, 1024, dtype=torch.bfloat16))
+    assert calls[-1] == "tile"
