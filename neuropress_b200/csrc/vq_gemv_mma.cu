@@ -74,6 +74,48 @@ __device__ __forceinline__ uint32_t to_operand(__half2 h) {
   }
 }
 
+// Eight consecutive indices of BITS bits as raw words (loaded one step ahead of their use) ...
+template <int BITS>
+struct RawIdx { uint32_t w[BITS / 4]; };
+
+template <int BITS>
+__device__ __forceinline__ RawIdx<BITS> load_raw(const uint8_t* __restrict__ p, int64_t chunk) {
+  RawIdx<BITS> r;
+  const uint8_t* q = p + chunk * BITS;
+  if constexpr (BITS == 16) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(q));
+    r.w[0] = v.x; r.w[1] = v.y; r.w[2] = v.z; r.w[3] = v.w;
+  } else if constexpr (BITS == 8) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(q));
+    r.w[0] = v.x; r.w[1] = v.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < BITS / 4; ++i) r.w[i] = __ldg(reinterpret_cast<const uint32_t*>(q) + i);
+  }
+  return r;
+}
+
+// ... and their expansion (LSB-first bit-stream, as read_index8).
+template <int BITS>
+__device__ __forceinline__ void expand(const RawIdx<BITS>& r, uint32_t (&idx)[8]) {
+  if constexpr (BITS == 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { idx[2 * i] = r.w[i] & 0xffffu; idx[2 * i + 1] = r.w[i] >> 16; }
+  } else if constexpr (BITS == 8) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) idx[i] = (r.w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int bit = i * BITS;
+      const uint32_t lo = r.w[bit / 32];
+      const uint32_t hi = (bit / 32 + 1 < BITS / 4) ? r.w[bit / 32 + 1] : 0u;
+      const uint64_t two = ((uint64_t)hi << 32) | lo;
+      idx[i] = (uint32_t)(two >> (bit % 32)) & ((1u << BITS) - 1u);
+    }
+  }
+}
+
 // Physical 16-byte chunk of logical chunk c (= vector index inside the K slice) in a row of
 // the activation tile: lanes t = 0..3 of a quad read chunks 8 t + s, which this spreads over
 // four different bank groups.
@@ -114,6 +156,24 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   const int n_groups = (a.N + 15) / 16;
   const int chunks_per_row = a.G >> 3;  // 8-index chunks per W row
   const bool has_res = a.has_res != 0, has_scale = a.has_scale != 0;
+  // Index words of one (row group, slice) item for this lane's two rows; the next item's are
+  // requested before the current item's gathers, so their latency is off the critical path.
+  struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; };
+  auto fetch = [&](Item& it, int rg_, int sl_) {
+    const int nl = rg_ * 16 + g, nh = nl + 8;
+    const int rl = nl < a.N ? nl : a.N - 1, rh = nh < a.N ? nh : a.N - 1;  // rows past N: row N-1
+    const int c0 = (warp * a.slices_per_warp + sl_) * 4 + t;               // chunk of 8 indices in the row
+    it.lo = load_raw<BITS>(a.packed, (int64_t)rl * chunks_per_row + c0);
+    it.hi = load_raw<BITS>(a.packed, (int64_t)rh * chunks_per_row + c0);
+    if (has_res) {
+      it.rlo = load_raw<8>(a.res_packed, (int64_t)rl * chunks_per_row + c0);
+      it.rhi = load_raw<8>(a.res_packed, (int64_t)rh * chunks_per_row + c0);
+    } else {
+      it.rlo.w[0] = it.rlo.w[1] = it.rhi.w[0] = it.rhi.w[1] = 0u;
+    }
+  };
+  Item nxt;
+  if ((int)blockIdx.x < n_groups) fetch(nxt, blockIdx.x, 0);
   int buf = 0;
   for (int rg = blockIdx.x; rg < n_groups; rg += gridDim.x, buf ^= 1) {
     const int n_lo = rg * 16 + g, n_hi = n_lo + 8;
@@ -132,16 +192,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
 
     for (int sl = 0; sl < a.slices_per_warp; ++sl) {
       const int slice = warp * a.slices_per_warp + sl;  // 32 vectors = 256 k
-      const int v0 = slice * 32 + 8 * t;                // this lane's 8 vectors of the slice
+      const Item cur = nxt;
+      if (sl + 1 < a.slices_per_warp) fetch(nxt, rg, sl + 1);
+      else if (rg + (int)gridDim.x < n_groups) fetch(nxt, rg + gridDim.x, 0);
       uint32_t idx_lo[8], idx_hi[8], rdx_lo[8], rdx_hi[8];
-      read_index8<BITS>(a.packed, (int64_t)r_lo * chunks_per_row + (v0 >> 3), idx_lo);
-      read_index8<BITS>(a.packed, (int64_t)r_hi * chunks_per_row + (v0 >> 3), idx_hi);
-#pragma unroll
-      for (int s = 0; s < 8; ++s) { rdx_lo[s] = 0; rdx_hi[s] = 0; }
-      if (has_res) {
-        read_index8<8>(a.res_packed, (int64_t)r_lo * chunks_per_row + (v0 >> 3), rdx_lo);
-        read_index8<8>(a.res_packed, (int64_t)r_hi * chunks_per_row + (v0 >> 3), rdx_hi);
-      }
+      expand<BITS>(cur.lo, idx_lo);
+      expand<BITS>(cur.hi, idx_hi);
+      expand<8>(cur.rlo, rdx_lo);
+      expand<8>(cur.rhi, rdx_hi);
       if (a.groups_per_codebook > 0) {  // a multiple of 32 vectors: constant over the slice
         const uint32_t off = (uint32_t)((slice * 32) / a.groups_per_codebook) * (uint32_t)a.num_centroids;
 #pragma unroll
