@@ -129,6 +129,7 @@ SMALL_BATCH_CASES = [
     (300, 1024, 4096, 16, 0, False, 512, False),
     (257, 2048, 65536, 16, 256, True, 0, True),
     (130, 4096, 4096, 16, 256, True, 2048, False),     # two codebooks of 2048 columns + residual
+    (5, 1024, 256, 8, 0, True, 0, True),               # fewer output rows than one 16-row group
 ]
 
 
