@@ -243,7 +243,7 @@ def run_ours(args) -> dict:
                 shared = PushGather(None, max(ROWS), N_OUT, torch.bfloat16, device)
                 for layer in layers:
                     layer.push = shared
-                gather_kind = "peer-store push (npb_allgather_push)"
+                gather_kind = "peer-store all-gather fused into the kernels (npb_gemm_allgather, npb_vq_gemv_allgather)"
             except Exception as exc:  # symmetric memory unavailable: keep NCCL
                 print(f"[bench] push gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
     xs_host = {m: make_activations(m, K_IN, torch.bfloat16, seed=m).pin_memory() for m in ROWS}
