@@ -330,23 +330,33 @@ Q_FUSED_MAX_ROWS = 384
 
 def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: int,
              group_size: int, zero_point: torch.Tensor | None = None,
-             bias: torch.Tensor | None = None) -> torch.Tensor:
+             bias: torch.Tensor | None = None, gather=None) -> torch.Tensor:
     """Drop-in for the reference's ``q_linear`` (kernels/__init__.py:109-151): ``x`` is
     ``[..., K]``, output ``[..., N]`` in ``x.dtype``.  The reference runs one GEMV kernel for
     every row count (q4_linear.cu:137-140); here rows are banded: GEMV up to 8 rows, then
-    decode once + dense GEMM (or, opt-in, the tile-dequant GEMM for the mid band)."""
+    decode once + dense GEMM (or, opt-in, the tile-dequant GEMM for the mid band).  ``gather``
+    (a ``sharding.PushGather``; not in the reference): the weight is an out-feature shard and the
+    all-gathered ``[..., N_full]`` is returned -- by the GEMM's own epilogue where it can."""
     k = w_pack.shape[1] * (8 // nbits)
     m = x.numel() // max(k, 1)
+    *leading, _ = x.shape
+
+    def pushed(y: torch.Tensor) -> torch.Tensor:
+        if gather is None:
+            return y
+        return gather(y.reshape(-1, y.shape[-1])).reshape(*leading, -1)
+
     if m <= GEMV_MAX_ROWS:
-        return q_gemv(x, w_pack, scale, nbits, group_size, zero_point, bias)
+        return pushed(q_gemv(x, w_pack, scale, nbits, group_size, zero_point, bias))
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("q_linear: more than 8 rows need fp16 or bf16 activations.")
     if (Q_TILE_DEQUANT_GEMM and m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0
             and group_size % 32 == 0):
-        return q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point, bias)
+        return pushed(q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point, bias))
     w = q_dequant(w_pack, scale, nbits, group_size, zero_point, x.dtype)
-    *leading, _ = x.shape
-    return gemm(x.reshape(-1, k), w, bias).reshape(*leading, w.shape[0])
+    if gather is not None and gather.accepts(m, x.dtype):
+        return gemm(x.reshape(-1, k), w, bias, gather=gather).reshape(*leading, -1)
+    return pushed(gemm(x.reshape(-1, k), w, bias).reshape(*leading, w.shape[0]))
 
 
 # ---------------------------------------------------------------------------

@@ -182,20 +182,22 @@ class NPLinear(nn.Module):
             self._bias_f32 = self.bias.detach().to(torch.float32).contiguous()
         return self._bias_f32
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, gather=None) -> torch.Tensor:
+        """``gather`` (not in the reference): a ``sharding.PushGather`` when this module holds an
+        out-feature shard; the all-gathered ``[..., N_full]`` is then returned."""
         if self.backend == LinearBackend.CUDA:
-            return self._forward_cuda(x)
+            return self._forward_cuda(x, gather)
         raise NotImplementedError(
             f"backend {self.backend.value!r} is not implemented by this package: only 'cuda' "
             "exists here; there is no eager, compiled or gemlite path."
         )
 
-    def _forward_cuda(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward_cuda(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """Banded CUDA forward (reference :732-761 runs one GEMV kernel for all row counts)."""
         from .. import kernels
 
         return kernels.q_linear(x.contiguous(), self.u8_blob, self.scale, self.nbits,
-                                self.group_size, self.zero_point, self._bias32())
+                                self.group_size, self.zero_point, self._bias32(), gather=gather)
 
     def extra_repr(self) -> str:
         return (f"in={self.in_features}, out={self.out_features}, nbits={self.nbits}, "

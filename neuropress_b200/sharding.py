@@ -218,7 +218,7 @@ class ShardedLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         push = getattr(self, "push", None) if self.gather else None
-        if push is not None and isinstance(self.local, NPVQLinear):
+        if push is not None and isinstance(self.local, NPVQLinear | NPLinear):
             # the local kernels store into every rank's buffer themselves where they can
             return self.local(x, gather=push)
         y = self.local(x)

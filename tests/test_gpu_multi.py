@@ -80,7 +80,28 @@ def _worker(rank: int, world: int, port: int, q) -> None:
         for rows, y in zip((2, 300), outs):
             assert_output_close(y, refs[rows][1], torch.bfloat16)
         assert layer.push.status() == 0
+
+        # a group-affine (HQQ-style) layer through the same fused all-gather
+        from neuropress_b200.nn import NPLinear
+        from neuropress_b200.synthetic import make_q_layer
+
+        qd = make_q_layer(512, 1024, group_size=64, asym=True, seed=5, bias=True)
+        qfull = NPLinear(qd.codes, qd.scale, 512, 1024, 64, 4, "asym", "auto", bias=qd.bias,
+                         zero_point=qd.zero_point)
+        qlayer = ShardedLinear.from_layer(qfull, rank, world).to(dev)
+        qlayer.push = layer.push          # same output shape: the buffers and flags are shared
+        for rows in (1, 8, 16, 300):
+            x = make_activations(rows, 1024, torch.bfloat16, seed=rows)
+            ref = oracle.q_forward_f64(x, qd.codes, qd.scale, 4, 64, qd.zero_point, qd.bias)
+            for _ in range(2):
+                y = qlayer(x.to(dev))
+                assert y.shape == (rows, 512)
+                assert_output_close(y, ref, torch.bfloat16)
+        assert qlayer.push.status() == 0
     except Exception as exc:  # report instead of hanging the peer
+        import traceback
+
+        traceback.print_exc()
         ok, msg = False, repr(exc)[:500]
     finally:
         q.put((rank, ok, msg))
@@ -100,7 +121,7 @@ def test_sharded_linear_two_gpus():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    results = sorted(q.get(timeout=300) for _ in procs)
+    results = sorted(q.get(timeout=150) for _ in procs)
     for p in procs:
         p.join(timeout=120)
     assert results == [(0, True, ""), (1, True, "")], results
