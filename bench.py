@@ -408,6 +408,28 @@ def run_ours(args) -> dict:
                            "launches_per_step": len(dec),
                            "share_of_step": round(share["npb_vq_decode"] / sum(share.values()), 3)}
     roofline = decode_roofline if dominant == "npb_vq_decode" else gemm_roofline
+    # The 1-row forward alone from a CUDA graph: its event-pair time above includes the host's
+    # enqueue latency, which a kernel this short does not hide.
+    gemv_graph_ms = None
+    if world == 1 and not args.eager:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=side):
+                    for c in range(N_COPIES):
+                        layers[c](xs[1])
+                g1.replay()
+                side.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(side)
+                g1.replay()
+                t1.record(side)
+                side.synchronize()
+            gemv_graph_ms = t0.elapsed_time(t1) / N_COPIES
+        except Exception as exc:  # measurement aid only
+            print(f"[bench] 1-row graph timing skipped ({exc!r})", file=sys.stderr)
     gemv_ms = kmean.get(("npb_vq_gemv", 1))
     gemv = None
     if gemv_ms:
@@ -415,6 +437,10 @@ def run_ours(args) -> dict:
         gemv = {"bound": "hbm", "kernel": "npb_vq_gemv at 1 row (vq_gemv_mma_kernel)", "achieved": round(gbs, 1),
                 "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
                 "launch_ms": round(gemv_ms, 5)}
+        if gemv_graph_ms:
+            gemv["graph_ms"] = round(gemv_graph_ms, 5)
+            gemv["graph_achieved"] = round(packed_bytes / (gemv_graph_ms * 1e-3) / 1e9, 1)
+            gemv["graph_frac"] = round(gemv["graph_achieved"] / peaks["hbm_gbs"], 4)
 
     line = {
         "metric": METRIC, "value": round(tokens_per_step * args.steps / (total_ms * 1e-3), 1),
