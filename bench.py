@@ -153,7 +153,7 @@ def build_layers(device, rank: int, world: int):
     """N_COPIES copies (different seeds) of the layer, this rank's rows only."""
     from neuropress_b200.nn import NPVQLinear, VQProxy
     from neuropress_b200.sharding import ShardedLinear
-    from neuropress_b200.synthetic import make_c2_layer
+    from synthetic import make_c2_layer
 
     layers = []
     packed_bytes = 0
@@ -201,7 +201,7 @@ def run_ours(args) -> dict:
     import torch.distributed as dist
 
     from neuropress_b200 import kernels
-    from neuropress_b200.synthetic import make_activations
+    from synthetic import make_activations
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -474,7 +474,7 @@ def run_ours(args) -> dict:
 
 # --------------------------------------------------------------------------- CPU ---
 def _cpu_layer():
-    from neuropress_b200.synthetic import make_activations, make_c2_layer
+    from synthetic import make_activations, make_c2_layer
 
     d = make_c2_layer(seed=0)
     xs = {m: make_activations(m, K_IN, torch.bfloat16, seed=m) for m in REF_ROWS}
@@ -538,7 +538,7 @@ def run_case(args) -> dict:
     """One band of the workload alone, a few launches: the command line profiled under ncu
     (small: four weight copies, one row count)."""
     from neuropress_b200 import kernels
-    from neuropress_b200.synthetic import make_activations, make_q_layer
+    from synthetic import make_activations, make_q_layer
 
     global N_COPIES
     N_COPIES = 4

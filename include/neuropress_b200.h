@@ -178,7 +178,7 @@ int npb_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_
  * Multi-GPU (new; the reference has no distributed code): all-gather of out-feature shards by
  * pushing.  This rank's src[M, n_local] (elem_bytes per element) is stored into columns
  * [rank*n_local, (rank+1)*n_local) of EVERY rank's [M, n_local*world] buffer; then each rank
- * flags every peer and waits (at most 2 s) for all peers' flags, so when the kernel ends the
+ * flags every peer and waits (bounded: npb_set_wait_limit_ns, 2 s by default) for all peers' flags, so when the kernel ends the
  * local buffer holds the full [M, N].  peer_out / peer_flags are DEVICE arrays of `world`
  * pointers (symmetric-memory buffer addresses of ranks 0..world-1); each rank's flag buffer
  * holds world + 3 zero-initialised uint32 words (per-peer epochs, a counter, a status word
@@ -219,21 +219,20 @@ int npb_vq_gemv_allgather(const npb_vq_weight* w, const void* x, int x_dtype, in
                           const npb_gather_sink* sink, npb_stream_t stream);
 
 
-/* Test hook, no reference counterpart: runs the tile decoder of npb_vq_gemm_fused on one
- * 128-row x 64-column W tile (rows [128*tile_n, +128), columns [64*k_block, +64)) and writes
- * the 16 KiB shared-memory image to out: row r occupies bytes [128 r, 128 r + 128), its
- * 16-byte chunk c is stored at chunk position c ^ (r & 7) (the 128-byte swizzle the tensor
- * core reads); rows past N are zero.  dtype NPB_BF16 or NPB_F16.  k_block == -1 decodes every
- * K block of the tile through the GEMM's shared-memory ring under its thread geometry and
- * writes K/64 consecutive 16 KiB images. */
-int npb_test_vq_decode_tile(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
-                            int dtype, void* out, npb_stream_t stream);
-
 /* Every wait inside the tensor-core GEMMs (on an mbarrier) is bounded; a kernel that gives up
  * records which role did so, frees its tensor memory and returns.  This call synchronises the
  * device, copies that record to *host_out (0 = no give-up since the last call), clears it, and
  * returns NPB_ERR_DEVICE_TIMEOUT if it was set.  No reference counterpart. */
 int npb_gemm_device_status(int* host_out);
+
+/* Limit of every bounded in-kernel wait of this library (the mbarrier waits of the GEMMs, the
+ * wait for the peers' flags in the all-gather kernels), in nanoseconds; 2 s by default,
+ * accepted range 1 us .. 60 s.  Process-wide, read when a kernel is launched.  A wait that
+ * runs out does not fault: the kernel records it (npb_gemm_device_status, the status word of
+ * the flag buffer) and returns.  Tests lower it to exercise exactly that path.  No reference
+ * counterpart. */
+int npb_set_wait_limit_ns(uint64_t ns);
+uint64_t npb_get_wait_limit_ns(void);
 
 #ifdef __cplusplus
 }

@@ -41,8 +41,9 @@ EXPORTED_SYMBOLS = (
     "npb_gemm_allgather",
     "npb_vq_gemv_allgather",
     "npb_rms_norm",
-    "npb_test_vq_decode_tile",
     "npb_gemm_device_status",
+    "npb_set_wait_limit_ns",
+    "npb_get_wait_limit_ns",
 )
 
 
@@ -129,8 +130,6 @@ def load_library() -> ctypes.CDLL:
     lib.npb_q_gemm_fused.argtypes = [q_p, *gemv_tail]
     lib.npb_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                              c_int, c_void_p]
-    lib.npb_test_vq_decode_tile.argtypes = [vq_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p,
-                                            c_void_p]
     lib.npb_allgather_push.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int,
                                        c_int, ctypes.c_uint32, c_void_p]
     sink_p = POINTER(GatherSinkStruct)
@@ -141,8 +140,11 @@ def load_library() -> ctypes.CDLL:
     lib.npb_rms_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_float, c_int,
                                  c_void_p]
     lib.npb_gemm_device_status.argtypes = [POINTER(c_int)]
+    lib.npb_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
+    lib.npb_get_wait_limit_ns.argtypes = []
     for name in EXPORTED_SYMBOLS[3:]:
         getattr(lib, name).restype = c_int
+    lib.npb_get_wait_limit_ns.restype = ctypes.c_uint64
     _lib = lib
     return lib
 

@@ -8,7 +8,7 @@
 // sees the counter complete knows all stores of this rank are fenced, publishes the flags with
 // release semantics and then polls its own flags with acquire semantics.  The kernel ends only
 // when all peers' slices are visible here, so later kernels on the stream can read the buffer.
-// The wait gives up after 2 s and records it in the status word (no trap, no endless spin).
+// The wait gives up after the wait limit (2 s unless npb_set_wait_limit_ns changed it) and records it in the status word (no trap, no endless spin).
 // Ranks must run on different GPUs: two ranks waiting on each other on one GPU may never be
 // resident together.
 #include "common.cuh"
@@ -24,6 +24,7 @@ struct PushArgs {
   int64_t M, row_local, row_full;
   int rank, world;
   uint32_t epoch;
+  uint64_t wait_ns;
 };
 
 // The flag words and the closing handshake are those of gather_sink.cuh; epoch 0 takes the
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(PushArgs a) {
   g.peer_out = nullptr;
   g.peer_flags = a.peer_flags;
   g.ld = 0; g.col0 = 0;
-  g.rank = a.rank; g.world = a.world; g.epoch = a.epoch;
+  g.rank = a.rank; g.world = a.world; g.epoch = a.epoch; g.wait_ns = a.wait_ns;
   if (threadIdx.x == 0) is_last = gather_cta_arrive(g, gridDim.x);
   __syncthreads();
   if (!is_last) return;
@@ -92,6 +93,7 @@ int allgather_push(const void* src, int64_t M, int64_t n_local, int64_t elem_byt
   a.rank = rank;
   a.world = world;
   a.epoch = epoch;
+  a.wait_ns = wait_limit_ns();
   const int64_t total = M * (row_local / 16) * world;
   int64_t blocks = (total + 255) / 256;
   const int cap = sm_count() * 2;

@@ -3,6 +3,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <tuple>
 #include <map>
@@ -38,9 +39,11 @@ int allgather_push(const void*, int64_t, int64_t, int64_t, const void*, const vo
                    cudaStream_t);
 int vq_linear_static_scratch(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t,
                              const float*, void*, cudaStream_t);
-int vq_decode_tile_probe(const npb_vq_weight*, int64_t, int64_t, int, int, int, void*, cudaStream_t);
 
 static thread_local char g_last_error[256] = "";
+
+static std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
+uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
 
 void set_last_cuda_error(cudaError_t e, const char* where) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorName(e),
@@ -203,12 +206,6 @@ int npb_q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t 
   return npb::q_gemm_fused(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
 }
 
-int npb_test_vq_decode_tile(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
-                            int dtype, void* out, npb_stream_t stream) {
-  return npb::vq_decode_tile_probe(w, N, K, tile_n, k_block, dtype, out,
-                                   static_cast<cudaStream_t>(stream));
-}
-
 int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
                                  int64_t N, int64_t K, const float* bias, void* y,
                                  npb_stream_t stream) {
@@ -232,6 +229,7 @@ static int to_sink(const npb_gather_sink* in, npb::GatherSink* out) {
   out->rank = in->rank;
   out->world = in->world;
   out->epoch = in->epoch;
+  out->wait_ns = npb::wait_limit_ns();
   return NPB_OK;
 }
 
@@ -256,5 +254,13 @@ int npb_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_
 }
 
 int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }
+
+int npb_set_wait_limit_ns(uint64_t ns) {
+  if (ns < 1000ull || ns > 60000000000ull) return NPB_ERR_INVALID_ARG;  // 1 us .. 60 s
+  npb::g_wait_limit_ns.store(ns, std::memory_order_relaxed);
+  return NPB_OK;
+}
+
+uint64_t npb_get_wait_limit_ns(void) { return npb::wait_limit_ns(); }
 
 }  // extern "C"

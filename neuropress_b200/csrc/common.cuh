@@ -35,6 +35,10 @@ inline bool aligned_to(const void* p, size_t a) {
   return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
 }
 
+// Limit, in nanoseconds, of every bounded in-kernel wait (mbarriers of the GEMMs, peer flags of
+// the all-gather): 2 s unless npb_set_wait_limit_ns changed it.  Read at launch time.
+uint64_t wait_limit_ns();
+
 // Number of SMs of the current device (cached per device id).
 int sm_count();
 // Opt a kernel into a large dynamic shared-memory size; cached by the caller.

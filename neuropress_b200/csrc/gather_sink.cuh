@@ -8,7 +8,7 @@
 //
 // Flag words of one rank (uint32, zero-initialised): [0, world) = epoch of the last call whose
 // slice from rank q has landed here, [world] = CTA counter, [world + 1] = status (1 = a wait
-// gave up after 2 s), [world + 2] = call counter (epoch source when the caller passes 0).
+// gave up after the wait limit, 2 s by default), [world + 2] = call counter (epoch source when the caller passes 0).
 #pragma once
 
 #include <stdint.h>
@@ -24,6 +24,7 @@ struct GatherSink {
   int64_t col0;                 // first destination column of this rank's slice
   int rank, world;
   uint32_t epoch;               // 0: use the call counter in the flag words
+  uint64_t wait_ns;             // limit of the wait for the peers' flags (set on the host side)
 };
 
 // Called by ONE thread of a CTA after that CTA's stores were fenced (__threadfence_system by
@@ -59,7 +60,7 @@ __device__ __forceinline__ void gather_signal_and_wait(const GatherSink& g, int 
         uint64_t now;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
         if (t0 == 0) t0 = now;
-        else if (now - t0 > 2000000000ull) {
+        else if (now - t0 > g.wait_ns) {
           atomicExch(reinterpret_cast<int*>(mine + g.world + 1), 1);
           break;
         }

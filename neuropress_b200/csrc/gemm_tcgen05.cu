@@ -44,7 +44,6 @@ constexpr int BM = 128;
 constexpr int BK = 64;            // 64 x 16-bit = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kAStageBytes = BM * BK * 2;                 // 16 KiB per 128-row A sub-tile
-constexpr uint64_t kWaitTimeoutNs = 2000000000ull;        // 2 s
 constexpr int kSmemCapAssumed = 232448;                   // opt-in dynamic shared memory per CTA on sm_100
 
 enum BMode { B_TMA = 0, B_VQ = 1, B_Q4 = 2 };
@@ -81,6 +80,7 @@ struct GemmParams {
   FusedVq vq;
   FusedQ4 q4;
   GatherSink sink;  // peer_out != null: y goes to every rank's buffer, then the handshake
+  uint64_t wait_ns;  // limit of every mbarrier wait (npb_set_wait_limit_ns; 2 s by default)
 };
 
 template <int BN, int MT>
@@ -306,6 +306,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* tmem_empty = tmem_full + 2;                            // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_got = abort_flag + 1;  // [2][4]: outcome of each epilogue warp's wait, per tile parity
   uint8_t* stage_base = smem + SmemLayout<BN, MT>::kBarrierBytes;
 
   const int warp = threadIdx.x >> 5;
@@ -345,7 +346,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int tm = t % p.tiles_m, tn = t / p.tiles_m;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs,
+          if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, p.wait_ns,
                                  BMODE == B_TMA ? 0u : 128u)) {
             atomicExch(&g_gemm_status, 1);
             ok = false;
@@ -374,14 +375,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int buf = (NBUF == 2) ? (it & 1) : 0;
         const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
-        if (!mbar_wait_bounded(&tmem_empty[buf], buf_ph ^ 1, abort_flag, kWaitTimeoutNs)) {
+        if (!mbar_wait_bounded(&tmem_empty[buf], buf_ph ^ 1, abort_flag, p.wait_ns)) {
           atomicExch(&g_gemm_status, 2);
           break;
         }
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * BUF_STRIDE;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, kWaitTimeoutNs)) {
+          if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.wait_ns)) {
             atomicExch(&g_gemm_status, 2);
             ok = false;
             break;
@@ -426,14 +427,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
       // All lanes wait (each needs the acquire), then agree on the outcome so that the
       // warp-collective tcgen05.ld below is never reached by part of a warp.
-      const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, kWaitTimeoutNs,
+      const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, p.wait_ns,
                                          BMODE == B_TMA ? 0u : 512u);
       if (gathered) {
-        // The four warps meet at a named barrier further down, so they must leave together: a
-        // wait that gave up has raised the CTA's abort flag, which all of them read after this
-        // barrier (every warp reaches it, whatever its own wait returned).
+        // The four warps meet at a named barrier further down, so they must leave together.
+        // The decision rests on words that only the epilogue warps write and that cannot change
+        // between the barrier and the reads: each warp publishes the outcome of its own wait
+        // (for this tile) before the barrier, all four read all four after it.  The CTA-wide
+        // abort flag is not used here: another role may raise it at any moment.
+        const bool warp_got = __all_sync(0xffffffffu, got);
+        volatile int* slot = epi_got + (it & 1) * 4;  // two sets: a fast warp may already write
+        if (lane == 0) slot[quad] = warp_got ? 1 : 0;  // the next tile's word while a slow one reads
+        __syncwarp();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*abort_flag) {
+        const bool all_got = slot[0] && slot[1] && slot[2] && slot[3];
+        if (!all_got) {
           atomicExch(&g_gemm_status, 3);
           break;
         }
@@ -457,8 +465,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int n0 = tn * BN + c * 32;
           if (m < p.M && n0 < p.N) {
             const int64_t off = (int64_t)m * ld + col0 + n0;
-            // destination bases are 16-byte aligned (checked on the host)
-            const bool full = (n0 + 32 <= p.N) && ((off * (int64_t)sizeof(T)) % 16 == 0);
+            // 16-byte stores only where the destination address itself is 16-byte aligned (an
+            // output that is a view at an odd offset takes the element-wise path)
+            const bool full = (n0 + 32 <= p.N) && ((reinterpret_cast<uintptr_t>(y + off) & 15u) == 0);
             if (full) {
               struct alignas(16) Out { T e[8]; } o[4];
 #pragma unroll
@@ -545,7 +554,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int tn = t / p.tiles_m;
         const int n = tn * BN + row;
         for (int kb = 0; kb < num_kb; ++kb) {
-          const bool got = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, kWaitTimeoutNs, 128u);
+          const bool got = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, p.wait_ns, 128u);
           if (!__all_sync(0xffffffffu, got)) {
             atomicExch(&g_gemm_status, 4);
             ok = false;
@@ -575,7 +584,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         auto step = [&](Q4Item<RPL>& cur, Q4Item<RPL>& nxt, int i) -> bool {
           if (i + S < total) q4_fetch<RPL>(nxt, p.q4, warp_n0(i + S), p.N, p.K, (i + S) % num_kb, lane);
           const uint32_t ph = (uint32_t)(i / S) & 1u;
-          const bool got = mbar_wait_bounded(&empty_bar[slot], ph ^ 1, abort_flag, kWaitTimeoutNs, 128u);
+          const bool got = mbar_wait_bounded(&empty_bar[slot], ph ^ 1, abort_flag, p.wait_ns, 128u);
           if (!__all_sync(0xffffffffu, got)) {
             atomicExch(&g_gemm_status, 4);
             return false;
@@ -679,6 +688,7 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
   } else {
     tb = ta;
   }
+  p.wait_ns = wait_limit_ns();
   p.tiles_m = (p.M + BM * MT - 1) / (BM * MT);
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
@@ -757,83 +767,6 @@ int fused_vq_bits(const npb_vq_weight* w, const FusedVq& v) {
   return 0;
 }
 
-// Test hook: decode one 128-row x 64-column W tile exactly as the fused GEMM's decoder warps
-// do (same function, same swizzled layout) and copy the 16 KiB tile image to global memory.
-template <typename T, int BITS>
-__global__ void __launch_bounds__(128) vq_tile_probe_kernel(FusedVq v, int N, int K, int tn, int kb,
-                                                            uint4* __restrict__ out) {
-  __shared__ __align__(1024) uint8_t tile[128 * 128];
-  const int row = threadIdx.x;
-  decode_vq_row<T, BITS>(v, tn * 128 + row, N, K / 8, kb, smem_u32(tile), row);
-  __syncthreads();
-  for (int i = threadIdx.x; i < 128 * 8; i += 128) out[i] = reinterpret_cast<const uint4*>(tile)[i];
-}
-
-// Test hook 2: the decoder under the fused GEMM's geometry -- a 320-thread CTA whose warps 6-9
-// decode every K block of one 128-row tile into a ring of 32 KiB stages in dynamic shared
-// memory (W tile in the upper 16 KiB of a stage, as in the GEMM), while the other warps copy
-// each finished tile to global memory.  No TMA, no tcgen05, no mbarriers: plain barriers.
-template <typename T, int BITS>
-__global__ void __launch_bounds__(320, 1) vq_ring_probe_kernel(FusedVq v, int N, int K, int tn, int stages,
-                                                               uint4* __restrict__ out) {
-  extern __shared__ uint8_t ring_raw[];
-  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~(uintptr_t)1023);
-  constexpr int kStage = 2 * kAStageBytes;   // A region (unused here) + W region
-  const int num_kb = K / BK;
-  const int warp = threadIdx.x >> 5;
-  for (int kb = 0; kb < num_kb; ++kb) {
-    const int s = kb % stages;
-    uint8_t* wtile = ring + (size_t)s * kStage + kAStageBytes;
-    if (warp >= 6) {
-      const int row = threadIdx.x - 6 * 32;
-      decode_vq_row<T, BITS>(v, tn * 128 + row, N, K / 8, kb, smem_u32(wtile), row);
-    }
-    __syncthreads();
-    if (warp < 6) {
-      for (int i = threadIdx.x; i < 128 * 8; i += 192)
-        out[(size_t)kb * 1024 + i] = reinterpret_cast<const uint4*>(wtile)[i];
-    }
-    __syncthreads();
-  }
-}
-
-template <typename T>
-int launch_ring_probe(const FusedVq& v, int vbits, int N, int K, int tn, void* out, cudaStream_t st) {
-  const int cap = max_dynamic_smem();
-  const int stages = SmemLayout<128, 1>::stages(cap);
-  const int smem = 1024 + stages * 2 * kAStageBytes;
-  uint4* o = static_cast<uint4*>(out);
-#define NPB_RING(BITS_)                                                                          \
-  do {                                                                                           \
-    auto kern = vq_ring_probe_kernel<T, BITS_>;                                                  \
-    NPB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    kern<<<1, 320, smem, st>>>(v, N, K, tn, stages, o);                                          \
-  } while (0)
-  switch (vbits) {
-    case 16: NPB_RING(16); break;
-    case 12: NPB_RING(12); break;
-    case 8: NPB_RING(8); break;
-    default: NPB_RING(0); break;
-  }
-#undef NPB_RING
-  NPB_LAUNCH_CHECK();
-  return NPB_OK;
-}
-
-template <typename T>
-int launch_tile_probe(const FusedVq& v, int vbits, int N, int K, int tn, int kb, void* out,
-                      cudaStream_t st) {
-  uint4* o = static_cast<uint4*>(out);
-  switch (vbits) {
-    case 16: vq_tile_probe_kernel<T, 16><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
-    case 12: vq_tile_probe_kernel<T, 12><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
-    case 8: vq_tile_probe_kernel<T, 8><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
-    default: vq_tile_probe_kernel<T, 0><<<1, 128, 0, st>>>(v, N, K, tn, kb, o); break;
-  }
-  NPB_LAUNCH_CHECK();
-  return NPB_OK;
-}
-
 int check_gemm_common(const void* x, const void* y, int64_t M, int64_t N, int64_t K, int dtype) {
   if (M < 0 || N < 0 || K < 0) return NPB_ERR_INVALID_ARG;
   if (dtype != NPB_BF16 && dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
@@ -908,28 +841,6 @@ int vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
     case 8: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 8>(x, p, st) : gemm_fused_mt<__half, B_VQ, 8>(x, p, st);
     default: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 0>(x, p, st) : gemm_fused_mt<__half, B_VQ, 0>(x, p, st);
   }
-}
-
-int vq_decode_tile_probe(const npb_vq_weight* w, int64_t N, int64_t K, int tile_n, int k_block,
-                         int dtype, void* out, cudaStream_t st) {
-  if (int rc = validate_vq(w, N, K)) return rc;
-  if (out == nullptr || w->vector_len != 8 || K % 64 != 0 || N <= 0) return NPB_ERR_UNSUPPORTED;
-  if (dtype != NPB_BF16 && dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
-  if (tile_n < 0 || (int64_t)tile_n * 128 >= N || k_block < -1 || (int64_t)k_block * 64 >= K)
-    return NPB_ERR_INVALID_ARG;
-  if (!aligned_to(out, 16) || !aligned_to(w->centroids, 16) ||
-      (w->res_centroids && !aligned_to(w->res_centroids, 16)))
-    return NPB_ERR_ALIGNMENT;
-  FusedVq v{};
-  fill_fused_vq(v, w, K);
-  const int vbits = fused_vq_bits(w, v);
-  if (vbits == 0 && v.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
-  if (k_block == -1)  // ring mode: all K blocks of the tile, out holds K/64 tile images
-    return dtype == NPB_BF16 ? launch_ring_probe<__nv_bfloat16>(v, vbits, (int)N, (int)K, tile_n, out, st)
-                             : launch_ring_probe<__half>(v, vbits, (int)N, (int)K, tile_n, out, st);
-  return dtype == NPB_BF16
-             ? launch_tile_probe<__nv_bfloat16>(v, vbits, (int)N, (int)K, tile_n, k_block, out, st)
-             : launch_tile_probe<__half>(v, vbits, (int)N, (int)K, tile_n, k_block, out, st);
 }
 
 int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,

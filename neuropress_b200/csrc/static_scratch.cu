@@ -13,6 +13,8 @@
 // calls must be ordered on one stream.  Nothing in the array has to start at zero: the decode
 // writes every element that the GEMM of the same call reads, and what an earlier call left
 // behind is never read.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace npb {
@@ -26,13 +28,16 @@ namespace {
 static __device__ __align__(256) unsigned char g_static_scratch[NPB_STATIC_SCRATCH_BYTES];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address;
-// the address of each device's copy is looked up once, with that device current.
+// the address of each device's copy is looked up once, with that device current.  The cache is
+// guarded, so host threads that make their first call on a device together do not race.
 void* g_scratch_addr[64] = {nullptr};
+std::mutex g_scratch_mutex;
 
 int scratch_address(void** out) {
   int dev = 0;
   NPB_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return NPB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (g_scratch_addr[dev] == nullptr) {
     void* p = nullptr;
     NPB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
@@ -53,6 +58,12 @@ int vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dtype,
   if (N > 0 && K > 0 && (uint64_t)N * (uint64_t)K > (uint64_t)NPB_STATIC_SCRATCH_BYTES / 2)
     return NPB_ERR_TOO_LARGE;
   if (M == 0 || N == 0) return NPB_OK;
+  // Everything the GEMM would reject is rejected here, before the decode is launched.
+  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (K == 0 || K % 8 != 0) return NPB_ERR_SHAPE;
+  if (!aligned_to(x, 16)) return NPB_ERR_ALIGNMENT;
+  if (M >= (int64_t)1 << 31 || N >= (int64_t)1 << 31 || K >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
+  if (int rc = validate_vq(w, N, K)) return rc;
   void* scratch = nullptr;
   if (int rc = scratch_address(&scratch)) return rc;
   if (int rc = vq_decode(w, N, K, scratch, x_dtype, st)) return rc;

@@ -383,37 +383,3 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.
                      x.shape[0], x.shape[1], float(eps), _cabi.dtype_code(x.dtype), _cabi.stream_ptr())
     _cabi.check(rc, "rms_norm")
     return out
-
-
-# ---------------------------------------------------------------------------
-# Test hook
-# ---------------------------------------------------------------------------
-
-
-def vq_decode_tile(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
-                   out_features: int, in_features: int, tile_n: int, k_block: int,
-                   dtype: torch.dtype, **ext) -> torch.Tensor:
-    """Run the fused GEMM's tile decoder on one 128 x 64 weight tile and return it
-    de-swizzled as a ``[128, 64]`` tensor of *dtype* (rows past ``out_features`` are zero).
-
-    The decoder stores 16-byte chunk ``c`` of tile row ``r`` at chunk position ``c ^ (r & 7)``
-    (the 128-byte swizzle the tensor core reads); this undoes that permutation on the host
-    side so the result can be compared with the dense decode.
-    """
-    ext = _vq_ext(ext)
-    _cabi.require_cuda("vq_decode_tile", packed_indices, centroids, ext.get("residual_indices"),
-                       ext.get("residual_centroids"), ext.get("row_scale"))
-    lib = _cabi.load_library()
-    w = _cabi.vq_struct(packed_indices, centroids, bits, **ext)
-    n_tiles = in_features // 64 if k_block == -1 else 1   # -1: every K block, through the ring
-    raw = torch.empty(n_tiles * 128 * 128, dtype=torch.uint8, device=packed_indices.device)
-    with torch.cuda.device(packed_indices.device):
-        rc = lib.npb_test_vq_decode_tile(w, out_features, in_features, tile_n, k_block,
-                                         _cabi.dtype_code(dtype), raw.data_ptr(), _cabi.stream_ptr())
-    _cabi.check(rc, "vq_decode_tile")
-    img = raw.view(n_tiles, 128, 8, 16)
-    r = torch.arange(128, device=raw.device).view(1, 128, 1)
-    c = torch.arange(8, device=raw.device).view(1, 1, 8)
-    pos = (c ^ (r & 7)).unsqueeze(-1).expand(n_tiles, 128, 8, 16)
-    out = torch.gather(img, 2, pos).reshape(n_tiles, 128, 128).view(dtype)
-    return out if k_block == -1 else out[0]

@@ -115,6 +115,7 @@ class NPLinear(nn.Module):
         if self.scale.numel() != n_groups:
             raise ValueError(f"scale must have {n_groups} elements.")
         self._bias_f32: torch.Tensor | None = None
+        self._bias_key = None
 
     @classmethod
     def from_linear(cls, linear: nn.Linear,
@@ -176,11 +177,18 @@ class NPLinear(nn.Module):
         return super()._apply(fn, recurse)
 
     def _bias32(self) -> torch.Tensor | None:
+        """fp32 copy of the bias.  The reference re-casts on every call
+        (vq_linear_wmma.cu:512-515); here the copy is kept and remade whenever the ``bias``
+        buffer was replaced, moved or written in place (``load_state_dict`` copies in place
+        and bumps the tensor's version counter)."""
         if self.bias is None:
             return None
-        if self._bias_f32 is None or self._bias_f32.device != self.bias.device:
+        key = (self.bias.data_ptr(), self.bias._version, self.bias.device)
+        if self._bias_f32 is None or self._bias_key != key:
             self._bias_f32 = self.bias.detach().to(torch.float32).contiguous()
+            self._bias_key = key
         return self._bias_f32
+
 
     def forward(self, x: torch.Tensor, gather=None) -> torch.Tensor:
         """``gather`` (not in the reference): a ``sharding.PushGather`` when this module holds an

@@ -235,6 +235,7 @@ class NPVQLinear(nn.Module):
         if self.row_scale is not None and self.row_scale.numel() != out_features:
             raise ValueError("row_scale must have out_features elements.")
         self._bias_f32: torch.Tensor | None = None
+        self._bias_key = None
 
     # ------------------------------------------------------------------ factory / serde
     @classmethod
@@ -332,14 +333,17 @@ class NPVQLinear(nn.Module):
         return d
 
     def _bias32(self) -> torch.Tensor | None:
-        """fp32 copy of the bias, made once per device instead of on every call."""
+        """fp32 copy of the bias.  The reference re-casts on every call
+        (vq_linear_wmma.cu:512-515); here the copy is kept and remade whenever the ``bias``
+        buffer was replaced, moved or written in place (``load_state_dict`` copies in place
+        and bumps the tensor's version counter)."""
         if self.bias is None:
             return None
-        b = self._bias_f32
-        if b is None or b.device != self.bias.device or b.data_ptr() == 0:
-            b = self.bias.detach().to(torch.float32).contiguous()
-            self._bias_f32 = b
-        return b
+        key = (self.bias.data_ptr(), self.bias._version, self.bias.device)
+        if self._bias_f32 is None or self._bias_key != key:
+            self._bias_f32 = self.bias.detach().to(torch.float32).contiguous()
+            self._bias_key = key
+        return self._bias_f32
 
     def _apply(self, fn, recurse: bool = True):
         self._bias_f32 = None

@@ -153,6 +153,12 @@ class PushGather:
     # measured on two B200s (2048 rows x 7168 columns: 124 us against 101 us + 72 us).
     fused_max_rows = int(os.environ.get("NEUROPRESS_B200_FUSED_GATHER_MAX_ROWS", str(1 << 30)))
 
+    def can_push(self, m: int, dtype: torch.dtype) -> bool:
+        """Whether an ``[m, N/P]`` result of *dtype* fits the buffers this gather was built
+        with.  Callers outside that envelope (more rows than ``max_rows``, another dtype) must
+        use the NCCL all-gather instead."""
+        return dtype == self.dtype and 0 < m <= self.max_rows
+
     def accepts(self, m: int, dtype: torch.dtype) -> bool:
         """Whether a kernel with a fused all-gather epilogue should be used for *m* rows."""
         return dtype == self.dtype and 0 < m <= min(self.max_rows, self.fused_max_rows)
@@ -218,6 +224,8 @@ class ShardedLinear(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         push = getattr(self, "push", None) if self.gather else None
+        if push is not None and not push.can_push(x.numel() // max(self.in_features, 1), x.dtype):
+            push = None  # outside what the peer-store buffers were built for: NCCL below
         if push is not None and isinstance(self.local, NPVQLinear | NPLinear):
             # the local kernels store into every rank's buffer themselves where they can
             return self.local(x, gather=push)

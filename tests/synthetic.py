@@ -13,7 +13,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from .transforms.vq_packing import IndexPacking
+from neuropress_b200.transforms.vq_packing import IndexPacking
 
 
 def _gen(seed: int, family: int) -> torch.Generator:

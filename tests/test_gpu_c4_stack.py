@@ -13,7 +13,7 @@ import torch
 
 import oracle
 from neuropress_b200.nn import NPVQLinear, VQProxy
-from neuropress_b200.synthetic import make_vq_layer
+from synthetic import make_vq_layer
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda", 0)

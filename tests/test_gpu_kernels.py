@@ -12,7 +12,7 @@ import torch
 import oracle
 from helpers import assert_output_close
 from neuropress_b200 import kernels
-from neuropress_b200.synthetic import make_activations, make_q_layer, make_vq_layer
+from synthetic import make_activations, make_q_layer, make_vq_layer
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -190,54 +190,6 @@ def test_dense_gemm_matches_fp32_reference(shape, dtype):
 
 
 # ----------------------------------------------------------------- tile-decode GEMMs ---
-TILE_CASES = [
-    (256, 512, 4096, 16, 0, False, 0),
-    (200, 1024, 4096, 12, 0, False, 0),
-    (384, 512, 65536, 16, 256, True, 0),
-    (128, 2048, 4096, 16, 0, False, 512),
-    (130, 256, 256, 8, 0, False, 0),
-    (72, 128, 1024, 10, 0, False, 0),
-]
-
-
-@pytest.mark.parametrize("case", TILE_CASES)
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_vq_tile_decoder_bit_exact(case, dtype):
-    """The decoder warps of the fused GEMM produce exactly the dense decode, tile by tile."""
-    N, K, NC, bits, res, scale, cpc = case
-    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K, residual_centroids=res,
-                          row_scale=scale, cols_per_codebook=cpc)
-    ref = _decode_ref(layer, dtype)
-    ref_pad = torch.zeros((N + 127) // 128 * 128, K, dtype=dtype)
-    ref_pad[:N] = ref
-    for tn in {0, (N - 1) // 128}:
-        for kb in {0, K // 64 - 1}:
-            tile = kernels.vq_decode_tile(layer.packed.to(DEV), layer.centroids.to(DEV), bits, N, K,
-                                          tn, kb, dtype, **_vq_ext_gpu(layer))
-            want = ref_pad[tn * 128:(tn + 1) * 128, kb * 64:(kb + 1) * 64]
-            torch.testing.assert_close(tile.cpu(), want, rtol=0, atol=0)
-
-
-@pytest.mark.parametrize("case", TILE_CASES)
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_vq_ring_decoder_bit_exact(case, dtype):
-    """The same decoder under the fused GEMM's thread / shared-memory geometry (320-thread CTA,
-    decode warps 6-9, ring of 32 KiB stages in dynamic shared memory), every K block of a tile."""
-    N, K, NC, bits, res, scale, cpc = case
-    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K, residual_centroids=res,
-                          row_scale=scale, cols_per_codebook=cpc)
-    ref = _decode_ref(layer, dtype)
-    ref_pad = torch.zeros((N + 127) // 128 * 128, K, dtype=dtype)
-    ref_pad[:N] = ref
-    for tn in {0, (N - 1) // 128}:
-        ring = kernels.vq_decode_tile(layer.packed.to(DEV), layer.centroids.to(DEV), bits, N, K, tn, -1,
-                                      dtype, **_vq_ext_gpu(layer))
-        want = ref_pad[tn * 128:(tn + 1) * 128].reshape(128, K // 64, 64).permute(1, 0, 2)
-        torch.testing.assert_close(ring.cpu(), want, rtol=0, atol=0)
-    from neuropress_b200 import _cabi
-    assert _cabi.gemm_device_status() == 0
-
-
 FUSED_CASES = [
     (256, 512, 4096, 16, 0, False, 0),
     (200, 1024, 4096, 12, 0, False, 0),

@@ -11,7 +11,7 @@ import torch
 import oracle
 from helpers import assert_output_close
 from neuropress_b200.nn import NPLinear, NPVQLinear, VQBackend, VQProxy
-from neuropress_b200.synthetic import make_activations, make_c2_layer, make_q_layer, make_vq_layer
+from synthetic import make_activations, make_c2_layer, make_q_layer, make_vq_layer
 from neuropress_b200.transforms.vq_packing import IndexPacking
 
 pytestmark = pytest.mark.gpu

@@ -31,7 +31,7 @@ def _worker(rank: int, world: int, port: int, q) -> None:
     from helpers import assert_output_close
     from neuropress_b200.nn import NPVQLinear, VQProxy
     from neuropress_b200.sharding import ShardedLinear
-    from neuropress_b200.synthetic import make_activations, make_vq_layer
+    from synthetic import make_activations, make_vq_layer
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -83,7 +83,7 @@ def _worker(rank: int, world: int, port: int, q) -> None:
 
         # a group-affine (HQQ-style) layer through the same fused all-gather
         from neuropress_b200.nn import NPLinear
-        from neuropress_b200.synthetic import make_q_layer
+        from synthetic import make_q_layer
 
         qd = make_q_layer(512, 1024, group_size=64, asym=True, seed=5, bias=True)
         qfull = NPLinear(qd.codes, qd.scale, 512, 1024, 64, 4, "asym", "auto", bias=qd.bias,

@@ -315,7 +315,7 @@ def test_small_batch_band_sits_between_the_gemv_and_the_tile_band(monkeypatch):
     """3..16 rows go to the fused kernel when the weight form fits the tensor-core small-batch
     kernel (vector length 8, 8/12/16-bit indices, K % 1024 == 0, fp16/bf16), else on to the
     tile-decode band as in the reference."""
-    from neuropress_b200.synthetic import make_vq_layer
+    from synthetic import make_vq_layer
 
     d = make_vq_layer(32, 1024, num_centroids=256, bits=8, seed=3)
     layer = NPVQLinear(VQProxy(d.centroids), d.packed, 8, 32, 1024, 8, backend="cuda_wmma")

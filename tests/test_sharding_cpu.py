@@ -14,7 +14,7 @@ import oracle
 from neuropress_b200.nn import NPLinear, NPVQLinear, VQProxy
 from neuropress_b200.sharding import (ShardedLinear, gather_outputs, shard_q_linear, shard_rows,
                                       shard_vq_linear)
-from neuropress_b200.synthetic import make_q_layer, make_vq_layer
+from synthetic import make_q_layer, make_vq_layer
 
 
 def test_shard_rows():
@@ -122,6 +122,9 @@ class _FakeGather:
         self.fused_rows, self.world, self.dtype, self.max_rows = fused_rows, world, torch.float32, 1 << 20
         self.calls = []
 
+    def can_push(self, m: int, dtype: torch.dtype) -> bool:
+        return dtype == self.dtype and 0 < m <= self.max_rows
+
     def accepts(self, m: int, dtype: torch.dtype) -> bool:
         return m <= self.fused_rows
 
@@ -153,3 +156,30 @@ def test_sharded_layer_hands_the_gather_to_the_shard_kernels(monkeypatch):
     assert y.shape == (1, 32) and seen[-1] == ("gemv", 1, True) and fake.calls == []
     y = layer(torch.zeros(2, 1, 64))                     # 2 rows: kernel cannot fuse -> push after it
     assert y.shape == (2, 1, 32) and seen[-1] == ("gemv", 2, False) and fake.calls == [("push", (2, 16))]
+
+
+def test_sharded_layer_outside_the_push_envelope_uses_the_collective(monkeypatch):
+    """More rows than the peer-store buffers hold, or another dtype: the shard runs locally and
+    the outputs go through ``gather_outputs`` (NCCL / gloo), never through the push gather."""
+    from neuropress_b200 import kernels, sharding
+
+    d = make_vq_layer(32, 64, num_centroids=16, bits=4, seed=1)
+    full = NPVQLinear(VQProxy(d.centroids), d.packed, 4, 32, 64, 8, backend="cuda")
+    layer = ShardedLinear.from_layer(full, 0, 2)
+    fake = _FakeGather(fused_rows=1)
+    fake.max_rows = 1
+    layer.push = fake
+    seen = []
+
+    def fake_gemv(x, packed, centroids, bits, n, bias, gather=None, **ext):
+        seen.append(gather)
+        return torch.zeros(x.shape[0], n, dtype=x.dtype)
+
+    monkeypatch.setattr(kernels, "vq_gemv", fake_gemv)
+    monkeypatch.setattr(sharding, "gather_outputs", lambda y, group=None: torch.cat([y, y], dim=-1))
+    y = layer(torch.zeros(2, 64))                        # 2 rows > max_rows = 1
+    assert y.shape == (2, 32) and seen[-1] is None and fake.calls == []
+    y = layer(torch.zeros(1, 64, dtype=torch.float16))   # dtype differs from the buffers'
+    assert y.shape == (1, 32) and seen[-1] is None and fake.calls == []
+    y = layer(torch.zeros(1, 64))                        # inside the envelope: fused as before
+    assert seen[-1] is fake

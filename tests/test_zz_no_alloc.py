@@ -16,7 +16,7 @@ import torch
 
 from neuropress_b200 import _cabi, kernels
 from neuropress_b200.kernels.static_scratch import MAX_WEIGHT_ELEMENTS, vq_linear_static_scratch
-from neuropress_b200.synthetic import make_activations, make_vq_layer
+from synthetic import make_activations, make_vq_layer
 
 DEV = "cuda"
 
