@@ -22,6 +22,9 @@ CSRC = PKG_DIR / "csrc"
 INCLUDE = PKG_DIR.parent / "include"
 OBJ_DIR = CSRC / "build"
 LIB_PATH = PKG_DIR / "libneuropress_b200.so"
+# Measurement probes of the benchmark: a library of their own, outside the product's C ABI.
+BENCH_LIB_PATH = PKG_DIR / "libneuropress_b200_bench.so"
+BENCH_SOURCES = ["bench_probes.cu"]
 
 SOURCES = [
     "c_api.cu",
@@ -30,6 +33,7 @@ SOURCES = [
     "q_kernels.cu",
     "q_gemv_mma.cu",
     "gemm_tcgen05.cu",
+    "vq_gemm_fused.cu",
     "static_scratch.cu",
     "allgather_push.cu", "rms_norm.cu", "vq_gemv_mma.cu",
 ]
@@ -71,16 +75,10 @@ def _compile_one(nvcc: str, src: Path, obj: Path, verbose: bool) -> str:
     return log
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every ``csrc/*.cu`` listed in ``SOURCES`` and link the shared library.
-
-    Returns the path of the library.  Objects are rebuilt only when their source or any
-    header is newer (``force`` rebuilds everything).
-    """
-    nvcc = find_nvcc()
+def _build_library(nvcc: str, names: list[str], lib_path: Path, force: bool, verbose: bool) -> Path:
     OBJ_DIR.mkdir(exist_ok=True)
     hdr_m = _newest_header_mtime()
-    sources = [CSRC / s for s in SOURCES]
+    sources = [CSRC / s for s in names]
     jobs = []
     for src in sources:
         obj = OBJ_DIR / (src.stem + ".o")
@@ -93,16 +91,29 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             for f in futs:
                 f.result()
     objs = [OBJ_DIR / (s.stem + ".o") for s in sources]
-    relink = bool(jobs) or not LIB_PATH.is_file() or any(
-        o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs
+    relink = bool(jobs) or not lib_path.is_file() or any(
+        o.stat().st_mtime > lib_path.stat().st_mtime for o in objs
     )
     if relink:
-        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs),
+        cmd = [nvcc, "-shared", "-o", str(lib_path), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "shared"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
-    return LIB_PATH
+    return lib_path
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every ``csrc/*.cu`` listed in ``SOURCES`` and link the shared library; then the
+    benchmark's probe library (``BENCH_SOURCES``).
+
+    Returns the path of the product library.  Objects are rebuilt only when their source or any
+    header is newer (``force`` rebuilds everything).
+    """
+    nvcc = find_nvcc()
+    path = _build_library(nvcc, SOURCES, LIB_PATH, force, verbose)
+    _build_library(nvcc, BENCH_SOURCES, BENCH_LIB_PATH, force, verbose)
+    return path
 
 
 def main(argv: list[str] | None = None) -> int:

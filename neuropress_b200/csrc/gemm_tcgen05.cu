@@ -1,29 +1,27 @@
 // Persistent warp-specialised tcgen05 GEMM  y[M,N] = x[M,K] . W[N,K]^T (+ bias)  for sm_100a,
-// in three flavours selected at compile time by where the W tile comes from:
+// in two flavours selected at compile time by where the W tile comes from:
 //
 //   B_TMA : W is a dense [N,K] matrix in HBM (the large-batch band after the one-pass decode);
 //           W tiles arrive by TMA like the x tiles.
-//   B_VQ  : W tiles are decoded from the packed index stream + codebook(s) by four decode
-//           warps straight into the 128B-swizzled shared-memory stage (mid-batch band; the
-//           dense weight never exists in HBM).  One 16-byte centroid (VL = 8) is exactly one
-//           swizzle chunk, so a decoded vector is a single st.shared.v4.
-//   B_Q4  : same, W tiles dequantised from 4-bit group-affine codes.
+//   B_Q4  : W tiles are dequantised from 4-bit group-affine codes by decode warps straight into
+//           the 128B-swizzled shared-memory stage (the dense weight never exists in HBM).
+//
+// (The tile-decode GEMM for vector-quantized weights is a kernel of its own: vq_gemm_fused.cu.)
 //
 // CTA = 128 x (MT*128 rows) x BN tile, K step 64.  Warp roles: warp 0 TMA producer, warp 1
 // TMEM owner + single-thread tcgen05.mma issuer, warps 2-5 epilogue (tcgen05.ld -> bias ->
-// T -> global), warps 6-9 (fused modes) B decoders.  smem ring of STAGES stages guarded by
+// T -> global), warps 6.. (fused mode) B decoders.  smem ring of STAGES stages guarded by
 // full/empty mbarriers; accumulators live in TMEM (MT*BN fp32 columns per buffer, two buffers
 // when they fit so the epilogue of tile i overlaps the MMAs of tile i+1).  Every mbarrier wait
 // is bounded: on give-up the CTA raises an abort flag, records it in g_gemm_status, lets the
 // outstanding copies land, frees its TMEM and returns.
 //
-// Bounds: fp32 accumulate of bf16/fp16 products; tensor-pipe bound for M >= ~1024, decode /
-// L2-gather bound in the fused modes.  FLOPs = 2*M*N*K; HBM bytes = operands once (x tiles are
-// re-read from L2).
+// Bounds: fp32 accumulate of bf16/fp16 products; tensor-pipe bound for M >= ~1024, decode bound
+// in the fused mode.  FLOPs = 2*M*N*K; HBM bytes = operands once (x tiles are re-read from L2).
 //
-// Stands in for: cuBLAS via F.linear (neuropress/nn/np_vq_linear.py:1148), the Triton
-// tile-decode GEMM (neuropress/kernels/vq_triton.py:37-116) and the wmma GEMM
-// (neuropress/kernels/vq_linear_wmma.cu:261-394).
+// Stands in for: cuBLAS via F.linear (neuropress/nn/np_vq_linear.py:1148) and, for group-affine
+// weights, the per-row GEMV the reference runs at every batch size
+// (neuropress/kernels/q4_linear.cu:80-131).
 #include <type_traits>
 
 #include "common.cuh"
@@ -46,23 +44,7 @@ constexpr int UMMA_K = 16;
 constexpr int kAStageBytes = BM * BK * 2;                 // 16 KiB per 128-row A sub-tile
 constexpr int kSmemCapAssumed = 232448;                   // opt-in dynamic shared memory per CTA on sm_100
 
-enum BMode { B_TMA = 0, B_VQ = 1, B_Q4 = 2 };
-
-struct FusedVq {
-  const uint8_t* packed;
-  int64_t packed_bytes;
-  const __half* centroids;
-  const uint8_t* res_packed;
-  int64_t res_bytes;
-  const __half* res_centroids;
-  const __half* row_scale;
-  int bits, res_bits, num_centroids, groups_per_codebook;
-  int cb_rows, res_rows;  // total codebook rows (n_codebooks * num_centroids), residual rows
-  // Whether the optional parts exist.  The pointers above are never null: an absent part
-  // aliases the main stream / codebook (see fill_fused_vq), so a load the compiler hoists
-  // above the test of these flags still reads mapped memory.
-  int has_res, has_scale;
-};
+enum BMode { B_TMA = 0, B_Q4 = 2 };
 
 struct FusedQ4 {
   const uint8_t* codes;
@@ -77,7 +59,6 @@ struct GemmParams {
   void* y;
   int M, N, K;
   int tiles_m, tiles_n;
-  FusedVq vq;
   FusedQ4 q4;
   GatherSink sink;  // peer_out != null: y goes to every rank's buffer, then the handshake
   uint64_t wait_ns;  // limit of every mbarrier wait (npb_set_wait_limit_ns; 2 s by default)
@@ -104,107 +85,10 @@ constexpr int q4_stages() {
 // ---- B tile decoders (fused modes) ---------------------------------------------------------
 // One decode thread owns one W row of the tile (BN == 128 == decode threads) and writes its
 // eight 16-byte chunks of the current 64-wide K block.
-template <typename T>
-__device__ __forceinline__ uint4 pack_half8(const __half2 (&h)[4]) {
-  if constexpr (sizeof(T) == 2 && !std::is_same<T, __nv_bfloat16>::value) {
-    uint4 o;
-    o.x = *reinterpret_cast<const uint32_t*>(&h[0]);
-    o.y = *reinterpret_cast<const uint32_t*>(&h[1]);
-    o.z = *reinterpret_cast<const uint32_t*>(&h[2]);
-    o.w = *reinterpret_cast<const uint32_t*>(&h[3]);
-    return o;
-  } else {
-    __nv_bfloat162 b[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h[i]);
-      b[i] = __floats2bfloat162_rn(f.x, f.y);  // same rounding as from_half<bf16>
-    }
-    uint4 o;
-    o.x = *reinterpret_cast<const uint32_t*>(&b[0]);
-    o.y = *reinterpret_cast<const uint32_t*>(&b[1]);
-    o.z = *reinterpret_cast<const uint32_t*>(&b[2]);
-    o.w = *reinterpret_cast<const uint32_t*>(&b[3]);
-    return o;
-  }
-}
-
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)
                : "memory");
-}
-
-template <typename T, int BITS>
-__device__ __forceinline__ void decode_vq_row(const FusedVq& p, int n, int N, int G, int kb,
-                                              uint32_t b_stage, int row) {
-  const uint32_t row_addr = b_stage + row * 128;
-  const int sw = row & 7;
-  if (n >= N) {
-    const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) st_shared_v4(row_addr + ((c ^ sw) << 4), z);
-    return;
-  }
-  uint32_t idx[8], ridx[8];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) ridx[c] = 0;
-  const bool has_res = p.has_res != 0;
-  if constexpr (BITS != 0) {
-    const int64_t chunk = (int64_t)n * (G >> 3) + kb;
-    // The decoder checks its own accesses: a stream offset or codebook index outside the
-    // buffers is recorded (status 10 / 11) and replaced by entry 0 instead of being read.
-    if ((chunk + 1) * BITS > p.packed_bytes || (has_res && (chunk + 1) * 8 > p.res_bytes)) {
-      atomicExch(&g_gemm_status, 10);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) { idx[c] = 0; ridx[c] = 0; }
-    } else {
-      read_index8<BITS>(p.packed, chunk, idx);
-      if (has_res) read_index8<8>(p.res_packed, chunk, ridx);
-    }
-  } else {
-    const int64_t v0 = (int64_t)n * G + kb * 8;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      idx[c] = read_index_generic(p.packed, p.packed_bytes, v0 + c, p.bits);
-      if (has_res) ridx[c] = read_index_generic(p.res_packed, p.res_bytes, v0 + c, p.res_bits);
-    }
-  }
-  if (p.groups_per_codebook > 0) {
-    const uint32_t off = (uint32_t)((kb * 8) / p.groups_per_codebook) * (uint32_t)p.num_centroids;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) idx[c] += off;
-  }
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    if (idx[c] >= (uint32_t)p.cb_rows || (has_res && ridx[c] >= (uint32_t)p.res_rows)) {
-      atomicExch(&g_gemm_status, 11);
-      idx[c] = 0;
-      ridx[c] = 0;
-    }
-  }
-  Half8 cv[8];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) cv[c] = ldg_vec(reinterpret_cast<const Half8*>(p.centroids) + idx[c]);
-  __half2 s2 = __float2half2_rn(1.f);
-  const bool has_scale = p.has_scale != 0;
-  if (has_scale) s2 = __half2half2(__ldg(p.row_scale + (has_scale ? n : 0)));
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    __half2 h[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = cv[c].h[i];
-    if (has_res) {
-      const Half8 r = ldg_vec(reinterpret_cast<const Half8*>(p.res_centroids) + ridx[c]);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) h[i] = __hadd2_rn(h[i], r.h[i]);
-    }
-    if (has_scale) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) h[i] = __hmul2_rn(h[i], s2);
-    }
-    st_shared_v4(row_addr + ((c ^ sw) << 4), pack_half8<T>(h));
-  }
 }
 
 // 4-bit group-affine decoder.  Every ring stage has its own decode warp(s): with S stages and
@@ -278,7 +162,7 @@ __device__ __forceinline__ void q4_emit(const Q4Item<RPL>& it, int n0, int N, ui
 // GATHER: the epilogue carries the fused all-gather (dense mode only); a separate instantiation
 // so that the plain kernels do not pay for its registers.
 template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER>
-__global__ void __launch_bounds__(BMODE == B_TMA ? 192 : BMODE == B_VQ ? 320 : 192 + 32 * kQ4DecodeWarps, 1)
+__global__ void __launch_bounds__(BMODE == B_TMA ? 192 : 192 + 32 * kQ4DecodeWarps, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p, const int stages) {
   constexpr int ACC_COLS = MT * BN;                       // fp32 columns per accumulator buffer
@@ -290,8 +174,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // Q4: S stages x R warps per stage (see the decoder notes); VQ: four warps share every stage.
   constexpr int kQ4Stages = q4_stages<BN, MT>();
   constexpr int kQ4WarpsPerStage = 4;
-  constexpr int kNumDecodeWarps = (BMODE == B_TMA) ? 0 : (BMODE == B_VQ) ? 4 : kQ4Stages * kQ4WarpsPerStage;
-  constexpr int kFullArrivals = (BMODE == B_TMA) ? 0 : (BMODE == B_VQ) ? 4 : kQ4WarpsPerStage;
+  constexpr int kNumDecodeWarps = (BMODE == B_TMA) ? 0 : kQ4Stages * kQ4WarpsPerStage;
+  constexpr int kFullArrivals = (BMODE == B_TMA) ? 0 : kQ4WarpsPerStage;
   static_assert(BMODE != B_Q4 || kNumDecodeWarps <= kQ4DecodeWarps, "decode warps of the Q4 launch");
   constexpr uint32_t kIdesc = umma_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
@@ -544,31 +428,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else {
     // ================= B decoders (fused modes only) =================
-    if constexpr (BMODE == B_VQ) {
-      const int row = threadIdx.x - 6 * 32;  // 0..127
-      const int G = p.K / 8;
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int tn = t / p.tiles_m;
-        const int n = tn * BN + row;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const bool got = mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, p.wait_ns, 128u);
-          if (!__all_sync(0xffffffffu, got)) {
-            atomicExch(&g_gemm_status, 4);
-            ok = false;
-            break;
-          }
-          const uint32_t b_stage = smem_u32(stage_base + (size_t)s * kStageBytes + MT * kAStageBytes);
-          decode_vq_row<T, BITS>(p.vq, n, p.N, G, kb, b_stage, row);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&full_bar[s]);
-          if (++s == stages) { s = 0; ph ^= 1; }
-        }
-      }
-    } else if constexpr (BMODE == B_Q4) {
+    if constexpr (BMODE == B_Q4) {
       constexpr int S = kQ4Stages, R = kQ4WarpsPerStage, RPL = 4 / R;
       const int dw = warp - 6;  // warps past S * R have no stage
       if (dw < S * R) {
@@ -693,7 +553,7 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  constexpr int threads = BMODE == B_TMA ? 192 : BMODE == B_VQ ? 320 : 192 + 32 * kQ4DecodeWarps;
+  constexpr int threads = BMODE == B_TMA ? 192 : 192 + 32 * kQ4DecodeWarps;
   kern<<<grid, threads, smem, st>>>(ta, tb, p, stages);
   NPB_LAUNCH_CHECK();
   return NPB_OK;
@@ -736,35 +596,6 @@ int gemm_fused_mt(const void* x, GemmParams p, cudaStream_t st) {
     case 2: return launch_gemm<T, 128, 2, BMODE, BITS>(x, nullptr, p, st);
     default: return launch_gemm<T, 128, 3, BMODE, BITS>(x, nullptr, p, st);
   }
-}
-
-void fill_fused_vq(FusedVq& v, const npb_vq_weight* w, int64_t K) {
-  v.packed = w->packed;
-  v.packed_bytes = w->packed_bytes;
-  v.centroids = static_cast<const __half*>(w->centroids);
-  v.has_res = w->res_packed != nullptr;
-  v.has_scale = w->row_scale != nullptr;
-  // Absent parts alias valid buffers and read entry 0 (never used in the result).
-  v.res_packed = v.has_res ? w->res_packed : w->packed;
-  v.res_bytes = v.has_res ? w->res_packed_bytes : 0;
-  v.res_centroids = v.has_res ? static_cast<const __half*>(w->res_centroids) : v.centroids;
-  v.row_scale = v.has_scale ? static_cast<const __half*>(w->row_scale) : v.centroids;
-  v.bits = w->bits;
-  v.res_bits = v.has_res ? w->res_bits : 0;
-  v.num_centroids = w->num_centroids;
-  v.groups_per_codebook = w->cols_per_codebook > 0 ? w->cols_per_codebook / 8 : 0;
-  v.cb_rows = w->num_centroids *
-              (w->cols_per_codebook > 0 ? (int)((K + w->cols_per_codebook - 1) / w->cols_per_codebook) : 1);
-  v.res_rows = w->res_num_centroids;
-}
-
-// Which index-read specialisation the tile decoder can use for this weight (0 = generic).
-int fused_vq_bits(const npb_vq_weight* w, const FusedVq& v) {
-  if ((w->bits == 16 || w->bits == 12 || w->bits == 8) &&
-      aligned_to(w->packed, index8_alignment(w->bits)) && (v.groups_per_codebook % 8 == 0) &&
-      (!w->res_packed || (w->res_bits == 8 && aligned_to(w->res_packed, 8))))
-    return w->bits;
-  return 0;
 }
 
 int check_gemm_common(const void* x, const void* y, int64_t M, int64_t N, int64_t K, int dtype) {
@@ -819,30 +650,6 @@ int gemm_gather(const void* x, const void* w, const float* bias, int64_t M, int6
   return gemm_impl(x, w, bias, nullptr, M, N, K, dtype, &sink, st);
 }
 
-int vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
-                  int64_t K, const float* bias, void* y, cudaStream_t st) {
-  if (int rc = validate_vq(w, N, K)) return rc;
-  if (int rc = check_gemm_common(x, y, M, N, K, x_dtype)) return rc;
-  if (M == 0 || N == 0) return NPB_OK;
-  if (w->vector_len != 8 || K % 64 != 0) return NPB_ERR_UNSUPPORTED;
-  if (!aligned_to(w->centroids, 16) || (w->res_centroids && !aligned_to(w->res_centroids, 16)))
-    return NPB_ERR_ALIGNMENT;
-  GemmParams p{};
-  p.bias = bias;
-  p.y = y;
-  p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  fill_fused_vq(p.vq, w, K);
-  const int vbits = fused_vq_bits(w, p.vq);
-  if (vbits == 0 && p.vq.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
-  const bool bf = x_dtype == NPB_BF16;
-  switch (vbits) {
-    case 16: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 16>(x, p, st) : gemm_fused_mt<__half, B_VQ, 16>(x, p, st);
-    case 12: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 12>(x, p, st) : gemm_fused_mt<__half, B_VQ, 12>(x, p, st);
-    case 8: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 8>(x, p, st) : gemm_fused_mt<__half, B_VQ, 8>(x, p, st);
-    default: return bf ? gemm_fused_mt<__nv_bfloat16, B_VQ, 0>(x, p, st) : gemm_fused_mt<__half, B_VQ, 0>(x, p, st);
-  }
-}
-
 int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
                  const float* bias, void* y, cudaStream_t st) {
   if (int rc = validate_q(w, N, K)) return rc;
@@ -864,6 +671,8 @@ int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, i
 }
 
 // Reads and clears the device-side give-up record of the GEMM kernels (synchronises).
+int vq_gemm_fused_device_status(int* host_out);  // vq_gemm_fused.cu keeps its own record
+
 int gemm_device_status(int* host_out) {
   int v = 0;
   NPB_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)));
@@ -871,6 +680,9 @@ int gemm_device_status(int* host_out) {
     const int zero = 0;
     NPB_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
   }
+  int vf = 0;
+  if (int rc = vq_gemm_fused_device_status(&vf)) return rc;
+  if (v == 0) v = vf;
   if (host_out) *host_out = v;
   return v == 0 ? NPB_OK : NPB_ERR_DEVICE_TIMEOUT;
 }

@@ -175,11 +175,9 @@ def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torc
 
 
 # Whether the mid-sized band runs the tile-decode GEMM (``npb_vq_gemm_fused``); when False it
-# runs the one-pass decode followed by the dense tensor-core GEMM.  Off: on a B200 the
-# decode + GEMM pair was faster on every shape measured (e.g. 14336 x 4096 with a 65536-entry
-# codebook, 128 rows: 82 us against 139 us) -- the centroid gathers bound both, and the
-# whole-GPU decode kernel keeps far more of them in flight than four decode warps per CTA.
-VQ_TILE_DECODE_GEMM = False
+# runs the one-pass decode followed by the dense tensor-core GEMM.
+VQ_TILE_DECODE_GEMM = True
+VQ_FUSED_MAX_ROWS = 384   # above this every weight tile would be decoded more than three times
 
 
 def vq_dequant_gemm(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
@@ -205,7 +203,7 @@ def vq_linear(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Te
         return vq_gemv(x, packed_indices, centroids, bits, None, bias, **ext)
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("vq_linear: more than 8 rows need fp16 or bf16 activations.")
-    if VQ_TILE_DECODE_GEMM and vector_len == 8 and x.shape[1] % 64 == 0:
+    if VQ_TILE_DECODE_GEMM and vector_len == 8 and x.shape[1] % 64 == 0 and x.shape[0] <= VQ_FUSED_MAX_ROWS:
         return vq_gemm_fused(x, packed_indices, centroids, bits, None, bias, **ext)
     return vq_dequant_gemm(x, packed_indices, centroids, bits, None, bias, **ext)
 

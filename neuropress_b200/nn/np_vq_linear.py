@@ -404,7 +404,9 @@ class NPVQLinear(nn.Module):
         from .. import kernels
 
         if (not kernels.VQ_TILE_DECODE_GEMM or x.dtype not in (torch.bfloat16, torch.float16)
-                or self.vector_len != 8 or self.in_features % 64):
+                or self.vector_len != 8 or self.in_features % 64
+                or (self.cols_per_codebook and self.cols_per_codebook % 64)
+                or (self.residual_indices is not None and self.residual_proxy.num_centroids > 256)):
             return self._forward_dequant_gemm(x, gather)
         x2, leading = self._flat(x)
         y = kernels.vq_gemm_fused(x2, self.packed_indices, self.proxy.centroids, self.bits,

@@ -28,3 +28,16 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Achieved output errors of the labelled parity cases (tolerance: 1e-2 * RMS + half an ulp)."""
+    try:
+        from helpers import MARGINS
+    except Exception:
+        return
+    if not MARGINS:
+        return
+    terminalreporter.write_sep("-", "parity margins: max|err|/RMS(ref), and the part beyond half an ulp of the output")
+    for label, rel, beyond in MARGINS:
+        terminalreporter.write_line(f"{label:<58s} {rel:9.5f}  {beyond:9.5f}")

@@ -9,6 +9,11 @@ import torch
 # up to half a unit in the last place of that dtype; the bound below adds exactly that.
 OUT_TOL = 1e-2
 
+# (label, max|err| / RMS(ref), how far the worst element is beyond its half-ulp allowance / RMS):
+# filled by assert_output_close, printed at the end of the run so the margin under the
+# tolerance is visible per case.
+MARGINS: list[tuple[str, float, float]] = []
+
 
 def half_ulp(ref64: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """Half a unit in the last place of *dtype* at each |ref| (0 for fp32)."""
@@ -19,8 +24,10 @@ def half_ulp(ref64: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return 0.5 * torch.exp2(torch.floor(torch.log2(a)) - mant)
 
 
-def assert_output_close(y: torch.Tensor, ref64: torch.Tensor, dtype: torch.dtype, tol: float = OUT_TOL):
-    """|y - ref| <= tol * RMS(ref) + half an ulp of the output dtype, elementwise."""
+def assert_output_close(y: torch.Tensor, ref64: torch.Tensor, dtype: torch.dtype, tol: float = OUT_TOL,
+                        label: str | None = None):
+    """|y - ref| <= tol * RMS(ref) + half an ulp of the output dtype, elementwise.  Returns
+    max|err| / RMS(ref); with *label* the achieved figures are kept for the end-of-run table."""
     y = y.detach().cpu().double()
     ref64 = ref64.detach().cpu().double()
     assert y.shape == ref64.shape, (y.shape, ref64.shape)
@@ -29,6 +36,9 @@ def assert_output_close(y: torch.Tensor, ref64: torch.Tensor, dtype: torch.dtype
     err = (y - ref64).abs()
     bound = tol * rms + half_ulp(ref64, dtype)
     worst = float((err - bound).max())
+    if label is not None:
+        beyond = float((err - half_ulp(ref64, dtype)).clamp_min(0).max()) / max(rms, 1e-30)
+        MARGINS.append((label, float(err.max()) / max(rms, 1e-30), beyond))
     assert worst <= 0, (
         f"max|err|={float(err.max()):.4g}, RMS(ref)={rms:.4g}, "
         f"max|err|/RMS={float(err.max()) / max(rms, 1e-30):.4g} exceeds the bound by {worst:.3g}"

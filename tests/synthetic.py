@@ -161,3 +161,30 @@ def make_c2_layer(seed: int = 0, out_features: int = 14336, in_features: int = 4
 
 
 C2_ROWS = (1, 2, 16, 128, 384, 2048)
+
+
+# ---- drawn on the device (the full-size layers of the benchmark and of the full-size tests) ----
+def device_bytes(n: int, device, seed: int) -> torch.Tensor:
+    """``n`` uniform random bytes drawn on the device from a seeded generator."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return torch.randint(0, 256, (n,), dtype=torch.uint8, device=device, generator=g)
+
+
+def pack_indices_device(idx: torch.Tensor, bits: int) -> torch.Tensor:
+    """LSB-first bit-stream of ``idx`` (any shape, flattened) for 16- or 12-bit indices, built on
+    the device: 16 bits = little-endian uint16; 12 bits = two indices a, b in three bytes
+    ``a & 255, (a >> 8) | ((b & 15) << 4), b >> 4``."""
+    v = idx.reshape(-1).to(torch.int32)
+    if bits == 16:
+        return torch.stack([v & 0xFF, v >> 8], dim=1).to(torch.uint8).reshape(-1)
+    if bits == 12 and v.numel() % 2 == 0:
+        a, b = v[0::2], v[1::2]
+        return torch.stack([a & 0xFF, (a >> 8) | ((b & 0xF) << 4), b >> 4], dim=1).to(torch.uint8).reshape(-1)
+    raise ValueError("pack_indices_device: 16-bit, or 12-bit with an even count")
+
+
+def device_normal(shape, device, seed: int, std: float = 1.0, dtype=torch.bfloat16) -> torch.Tensor:
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return (torch.randn(shape, device=device, generator=g) * std).to(dtype)
