@@ -45,8 +45,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kAStageBytes = BM * BK * 2;
-constexpr int kMaxGroups = 4;                       // decode groups = ring stages
-constexpr int kDecodeWarps = 4 * kMaxGroups;
+constexpr int kDecodeWarps = 16;
+constexpr int kMaxGroups = kDecodeWarps;            // decode groups = ring stages (1, 2 or 4 warps each)
 constexpr int kThreads = 192 + 32 * kDecodeWarps;   // 704
 constexpr int kBarrierBytes = 1024;
 constexpr int kResTableBytes = 256 * 16;
@@ -64,7 +64,7 @@ struct FusedParams {
   uint64_t wait_ns;
   int bits, res_bits, num_centroids, groups_per_codebook, cb_rows, res_rows;
   int has_res, has_scale;
-  int M, N, K, BN, tiles_m, tiles_n, groups;
+  int M, N, K, BN, tiles_m, tiles_n, groups, warps_per_group;
 };
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
@@ -225,7 +225,7 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < G; ++s) {
-      mbar_init(&full_bar[s], 1 + 4);   // TMA producer's expect_tx arrive + one arrive per decode warp
+      mbar_init(&full_bar[s], 1 + p.warps_per_group);  // TMA producer's expect_tx arrive + one per decode warp
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -367,9 +367,10 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
   } else {
     // ================= decode warps =================
     const int dw = warp - 6;
-    const int grp = dw >> 2, part = dw & 3;   // group = ring stage; four warps share its BN rows
+    const int wpg = p.warps_per_group;        // 1, 2 or 4 warps share a stage's BN rows
+    const int grp = dw / wpg, part = dw - grp * wpg;
     if (grp < G) {
-      const int rows_per_warp = BN >> 2;      // BN is a multiple of 16
+      const int rows_per_warp = BN / wpg;
       const int row0 = part * rows_per_warp;
       const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
       const int total = my_tiles * num_kb;    // the CTA's (tile, k block) items in ring order
@@ -481,8 +482,15 @@ int launch(const void* x, FusedParams p, cudaStream_t st) {
   p.tiles_n = (p.N + p.BN - 1) / p.BN;
   const int stage_bytes = MT * kAStageBytes + p.BN * 128;
   const int cap = max_dynamic_smem();
+  // Narrow tiles have few gathers per stage and are bound by the latency of one decode; they get
+  // more, smaller groups (more stages decoded concurrently): a warp covers up to 64 rows.
+  int wpg = 4;
+  if (p.BN <= 32) wpg = 1;
+  else if (p.BN <= 64) wpg = 2;
+  if (p.BN % wpg != 0) wpg = 4;
+  p.warps_per_group = wpg;
   int groups = (cap - kBarrierBytes - kResTableBytes - 1024) / stage_bytes;
-  if (groups > kMaxGroups) groups = kMaxGroups;
+  if (groups > kDecodeWarps / wpg) groups = kDecodeWarps / wpg;
   if (groups < 2) return NPB_ERR_UNSUPPORTED;
   p.groups = groups;
   const int smem = kBarrierBytes + kResTableBytes + 1024 + groups * stage_bytes;
