@@ -174,6 +174,28 @@ int npb_vq_linear_static_scratch(const npb_vq_weight* w, const void* x, int x_dt
 int npb_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_t H, float eps,
                  int dtype, npb_stream_t stream);
 
+/* ---- embedding lookups (only the rows the token ids select are decoded) ------------- */
+
+/* out[t, :] = decode(row ids[t]) of a VQ-compressed embedding table, t < T.  all_indices is the
+ * pre-unpacked [V, G] table of 16-bit codebook indices the reference keeps
+ * (neuropress/nn/np_vq_embedding.py:88, read as unsigned), centroids fp16 [num_centroids,
+ * vector_len] with vector_len 4 or 8, inv_perm int64 [G * vector_len] or NULL (output column c
+ * takes decoded column inv_perm[c]), scale applied to the fp16 value and rounded to fp16, then one
+ * conversion to out_dtype: the arithmetic of NPVQEmbedding.forward (:119-141).  ids int64; an id
+ * outside [0, V) yields a zero row. */
+int npb_vq_embedding(const int64_t* ids, int64_t T, const uint16_t* all_indices, int64_t V, int64_t G,
+                     const void* centroids, int32_t num_centroids, int32_t vector_len,
+                     const int64_t* inv_perm, float scale, void* out, int out_dtype,
+                     npb_stream_t stream);
+
+/* out[t, :] = embed_scale * T(fp16((q - zp) * s)) for the rows ids[t] of a group-affine table
+ * w (codes [V, D * nbits / 8], fp16 scale / zero-point [V * D / group_size]); the row
+ * padding_idx (-1: none) and ids outside [0, V) yield zeros.  Replaces _emb_dequant and
+ * NPEmbedding.forward (neuropress/nn/np_embedding.py:120-183, 449-473). */
+int npb_q_embedding(const int64_t* ids, int64_t T, const npb_q_weight* w, int64_t V, int64_t D,
+                    int64_t padding_idx, float embed_scale, void* out, int out_dtype,
+                    npb_stream_t stream);
+
 /*
  * Multi-GPU (new; the reference has no distributed code): all-gather of out-feature shards by
  * pushing.  This rank's src[M, n_local] (elem_bytes per element) is stored into columns

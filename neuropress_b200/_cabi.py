@@ -41,6 +41,8 @@ EXPORTED_SYMBOLS = (
     "npb_gemm_allgather",
     "npb_vq_gemv_allgather",
     "npb_rms_norm",
+    "npb_vq_embedding",
+    "npb_q_embedding",
     "npb_gemm_device_status",
     "npb_set_wait_limit_ns",
     "npb_get_wait_limit_ns",
@@ -139,6 +141,10 @@ def load_library() -> ctypes.CDLL:
                                           sink_p, c_void_p]
     lib.npb_rms_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_float, c_int,
                                  c_void_p]
+    lib.npb_vq_embedding.argtypes = [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int32, c_int32,
+                                     c_void_p, ctypes.c_float, c_void_p, c_int, c_void_p]
+    lib.npb_q_embedding.argtypes = [c_void_p, c_int64, q_p, c_int64, c_int64, c_int64, ctypes.c_float, c_void_p,
+                                    c_int, c_void_p]
     lib.npb_gemm_device_status.argtypes = [POINTER(c_int)]
     lib.npb_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     lib.npb_get_wait_limit_ns.argtypes = []

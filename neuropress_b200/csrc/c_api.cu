@@ -31,6 +31,10 @@ int gemm_device_status(int*);
 int vq_gemv_mma(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
                 const GatherSink*, cudaStream_t);
 int rms_norm(const void*, const void*, void*, int64_t, int64_t, float, int, cudaStream_t);
+int vq_embedding(const int64_t*, int64_t, const uint16_t*, int64_t, int64_t, const void*, int, int, const int64_t*,
+                 float, void*, int, cudaStream_t);
+int q_embedding(const int64_t*, int64_t, const npb_q_weight*, int64_t, int64_t, int64_t, float, void*, int,
+                cudaStream_t);
 int gemm_gather(const void*, const void*, const float*, int64_t, int64_t, int64_t, int, const GatherSink&,
                 cudaStream_t);
 int vq_gemv_gather(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
@@ -251,6 +255,19 @@ int npb_vq_gemv_allgather(const npb_vq_weight* w, const void* x, int x_dtype, in
 int npb_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_t H, float eps,
                  int dtype, npb_stream_t stream) {
   return npb::rms_norm(x, weight, out, M, H, eps, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_embedding(const int64_t* ids, int64_t T, const uint16_t* all_indices, int64_t V, int64_t G,
+                     const void* centroids, int32_t num_centroids, int32_t vector_len, const int64_t* inv_perm,
+                     float scale, void* out, int out_dtype, npb_stream_t stream) {
+  return npb::vq_embedding(ids, T, all_indices, V, G, centroids, num_centroids, vector_len, inv_perm, scale, out,
+                           out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int npb_q_embedding(const int64_t* ids, int64_t T, const npb_q_weight* w, int64_t V, int64_t D,
+                    int64_t padding_idx, float embed_scale, void* out, int out_dtype, npb_stream_t stream) {
+  return npb::q_embedding(ids, T, w, V, D, padding_idx, embed_scale, out, out_dtype,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int npb_gemm_device_status(int* host_out) { return npb::gemm_device_status(host_out); }

@@ -96,25 +96,34 @@ class AutoKernelLowering(KernelLowering):
                    embedding_backend=cfg.embedding_backend, norm_backend=cfg.norm_backend)
 
     def apply(self, model: nn.Module) -> None:
+        """The five passes in the reference's order (:200-249): affine embeddings, affine
+        linears, VQ linears, VQ embeddings, RMSNorm modules."""
+        from .nn.np_embedding import NPEmbedding, linearize_qtensor_embeddings
         from .nn.np_linear import NPLinear, linearize_qtensor_weights
+        from .nn.np_vq_embedding import NPVQEmbedding, linearize_vq_embeddings
         from .nn.np_vq_linear import NPVQLinear, linearize_vq_weights
 
+        linearize_qtensor_embeddings(model, backend=self.embedding_backend)
         linearize_qtensor_weights(model, backend=self.linear_backend)
         linearize_vq_weights(model, backend=self.vq_backend)
+        linearize_vq_embeddings(model)
+        n_norms = 0
         if self.norm_backend in ("auto", "cuda"):  # "default" keeps the model's own norms
             from .nn.np_rms_norm import linearize_rms_norms
 
             n_norms = linearize_rms_norms(model)
-            if n_norms:
-                LOGGER.info("Kernel lowering: %d RMSNorm module(s) fused", n_norms)
         # A lowered lm_head no longer shares storage with the embedding (reference :221-227).
         if hasattr(model, "config") and hasattr(model.config, "tie_word_embeddings"):
             model.config.tie_word_embeddings = False
         counts: dict[str, int] = {}
         for m in model.modules():
-            if isinstance(m, NPLinear | NPVQLinear):
+            if isinstance(m, NPLinear | NPVQLinear | NPEmbedding):
                 key = f"{type(m).__name__}({m.backend.value})"
                 counts[key] = counts.get(key, 0) + 1
+            elif isinstance(m, NPVQEmbedding):
+                counts["NPVQEmbedding"] = counts.get("NPVQEmbedding", 0) + 1
+        if n_norms:
+            counts["NPRMSNorm(cuda)"] = n_norms
         if counts:
             LOGGER.warning("Kernel lowering applied: %s",
                            ", ".join(f"{v}x {k}" for k, v in sorted(counts.items())))
@@ -123,11 +132,13 @@ class AutoKernelLowering(KernelLowering):
 
 
 def is_lowered(model: nn.Module) -> bool:
-    """``True`` if *model* contains an :class:`NPLinear` or :class:`NPVQLinear`."""
+    """``True`` if *model* contains any lowered NP* module (reference :257-277)."""
+    from .nn.np_embedding import NPEmbedding
     from .nn.np_linear import NPLinear
+    from .nn.np_vq_embedding import NPVQEmbedding
     from .nn.np_vq_linear import NPVQLinear
 
-    return any(isinstance(m, NPLinear | NPVQLinear) for m in model.modules())
+    return any(isinstance(m, NPLinear | NPVQLinear | NPEmbedding | NPVQEmbedding) for m in model.modules())
 
 
 def unlower_model(model: nn.Module) -> None:
@@ -151,7 +162,29 @@ def unlower_model(model: nn.Module) -> None:
     for name, new_mod in replacements:
         parent = model.get_submodule(name.rsplit(".", 1)[0]) if "." in name else model
         setattr(parent, name.rsplit(".", 1)[-1], new_mod)
-    for pname in [n for n, _ in model.named_children() if n.startswith("_vq_proxy_")]:
+    # embeddings go back to nn.Embedding shells holding their QTensor (reference :316-352)
+    from .nn.np_embedding import NPEmbedding
+    from .nn.np_vq_embedding import NPVQEmbedding
+
+    for name, module in list(model.named_modules()):
+        if not isinstance(module, NPEmbedding | NPVQEmbedding):
+            continue
+        qtensor = module.to_qtensor()
+        if isinstance(module, NPEmbedding):
+            vocab, dim, pad = module.num_embeddings, module.embedding_dim, module.padding_idx
+        else:
+            vocab, dim, pad = module.all_indices.shape[0], module.embedding_dim, None
+        with torch.device("meta"):
+            emb = nn.Embedding(vocab, dim, padding_idx=pad)
+        emb._parameters["weight"] = qtensor
+        scale = module.embed_scale if isinstance(module, NPEmbedding) else module.scale
+        if scale != 1.0:
+            emb.embed_scale = scale
+        parent = model.get_submodule(name.rsplit(".", 1)[0]) if "." in name else model
+        setattr(parent, name.rsplit(".", 1)[-1], emb)
+        replacements.append((name, emb))
+    for pname in [n for n, _ in model.named_children()
+                  if n.startswith("_vq_proxy_") or n.startswith("_vq_emb_proxy_")]:
         delattr(model, pname)
     # fused norms go back to the modules they replaced
     from .nn.np_rms_norm import NPRMSNorm

@@ -381,3 +381,60 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.
                      x.shape[0], x.shape[1], float(eps), _cabi.dtype_code(x.dtype), _cabi.stream_ptr())
     _cabi.check(rc, "rms_norm")
     return out
+
+
+# ---------------------------------------------------------------------------
+# Embedding lookups
+# ---------------------------------------------------------------------------
+
+
+def vq_embedding(input_ids: torch.Tensor, all_indices: torch.Tensor, centroids: torch.Tensor,
+                 embedding_dim: int, scale: float = 1.0, inv_perm: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Rows ``input_ids`` of a VQ-compressed embedding table, ``[..., embedding_dim]``.
+    ``all_indices`` is the ``[vocab, n_groups]`` 16-bit index table, ``centroids`` the fp16
+    ``[NC, VL]`` codebook; arithmetic as ``NPVQEmbedding.forward`` of the reference
+    (np_vq_embedding.py:119-141).  Output dtype ``out_dtype`` (fp16 when ``None``)."""
+    _cabi.require_cuda("vq_embedding", input_ids, all_indices, centroids, inv_perm)
+    if all_indices.dtype not in (torch.int16, torch.uint16) or all_indices.dim() != 2:
+        raise RuntimeError("vq_embedding: all_indices must be a [vocab, n_groups] 16-bit tensor.")
+    if centroids.dtype != torch.float16 or centroids.dim() != 2:
+        raise RuntimeError("vq_embedding: centroids must be a [NC, VL] float16 tensor.")
+    v, g = all_indices.shape
+    vl = centroids.shape[1]
+    if g * vl != embedding_dim:
+        raise RuntimeError("vq_embedding: n_groups * vector_len must equal embedding_dim.")
+    if inv_perm is not None and (inv_perm.dtype != torch.int64 or inv_perm.numel() != embedding_dim):
+        raise RuntimeError("vq_embedding: inv_perm must be int64 with embedding_dim elements.")
+    lib = _cabi.load_library()
+    ids = input_ids.reshape(-1).to(torch.int64).contiguous()
+    dt = out_dtype if out_dtype is not None else torch.float16
+    out = torch.empty((ids.numel(), embedding_dim), dtype=dt, device=ids.device)
+    with torch.cuda.device(ids.device):
+        rc = _launch("npb_vq_embedding", lib.npb_vq_embedding, ids.data_ptr(), ids.numel(),
+                     all_indices.data_ptr(), v, g, centroids.data_ptr(), centroids.shape[0], vl,
+                     None if inv_perm is None else inv_perm.data_ptr(), float(scale), out.data_ptr(),
+                     _cabi.dtype_code(dt), _cabi.stream_ptr())
+    _cabi.check(rc, "vq_embedding")
+    return out.reshape(*input_ids.shape, embedding_dim)
+
+
+def q_embedding(input_ids: torch.Tensor, u8_blob: torch.Tensor, scale: torch.Tensor, nbits: int,
+                group_size: int, zero_point: torch.Tensor | None = None, padding_idx: int | None = None,
+                embed_scale: float = 1.0, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Rows ``input_ids`` of a group-affine embedding table, gathered in packed space and
+    dequantised: ``_emb_dequant`` + the tail of ``NPEmbedding.forward`` of the reference
+    (np_embedding.py:120-183, 449-473).  Output dtype ``out_dtype`` (fp16 when ``None``)."""
+    _cabi.require_cuda("q_embedding", input_ids, u8_blob, scale, zero_point)
+    v, d = _q_prepare("q_embedding", u8_blob, scale, zero_point, nbits, group_size)
+    lib = _cabi.load_library()
+    w = _cabi.q_struct(u8_blob, scale, zero_point, nbits, group_size)
+    ids = input_ids.reshape(-1).to(torch.int64).contiguous()
+    dt = out_dtype if out_dtype is not None else torch.float16
+    out = torch.empty((ids.numel(), d), dtype=dt, device=ids.device)
+    with torch.cuda.device(ids.device):
+        rc = _launch("npb_q_embedding", lib.npb_q_embedding, ids.data_ptr(), ids.numel(), w, v, d,
+                     -1 if padding_idx is None else int(padding_idx), float(embed_scale), out.data_ptr(),
+                     _cabi.dtype_code(dt), _cabi.stream_ptr())
+    _cabi.check(rc, "q_embedding")
+    return out.reshape(*input_ids.shape, d)

@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 import torch
 
 
-@dataclass
+@dataclass(eq=False)
 class VQScheme:
     """Attributes read by ``NPVQLinear.from_qtensor_linear`` (reference np_vq_linear.py:863-879)."""
 
@@ -28,9 +28,10 @@ class VQScheme:
     use_tiered: bool = False
     tier_bits: list[int] | None = None
     zero_escape: bool = False
+    original_shape: tuple[int, int] | None = None   # read by linearize_vq_embeddings (np_vq_embedding.py:206-212)
 
 
-@dataclass
+@dataclass(eq=False)
 class VQQTensor:
     """A VQ weight: ``u8_blob`` (LSB-first index bit-stream) + ``qscheme``."""
 
@@ -43,7 +44,7 @@ class VQQTensor:
         return {"type": "QTensorTractVQ", "shape": list(self.shape), **self.meta}
 
 
-@dataclass
+@dataclass(eq=False)
 class AffineScheme:
     """Attributes read by ``NPLinear.from_linear`` (reference np_linear.py:573-610)."""
 
@@ -56,7 +57,7 @@ class AffineScheme:
         return self.zero_point
 
 
-@dataclass
+@dataclass(eq=False)
 class AffineQTensor:
     """A group-affine weight: ``u8_blob`` is ``[N, K*n_bits/8]`` codes packed LSB-first."""
 

@@ -20,6 +20,8 @@ Reference locations restated here (paths inside the reference project):
   * nibble unpack               neuropress/nn/np_linear.py:78-96
   * group-affine decode+linear  neuropress/nn/np_linear.py:298-353
                                 neuropress/kernels/q4_linear.cu:80-131
+  * embedding lookups           neuropress/nn/np_vq_embedding.py:119-141
+                                neuropress/nn/np_embedding.py:120-183, 449-503
 """
 
 from __future__ import annotations
@@ -248,6 +250,61 @@ def rel_max_err(y: torch.Tensor, y_ref: torch.Tensor) -> float:
     r = y_ref.detach().cpu().double()
     rms = float(torch.sqrt(torch.mean(r * r)))
     return float((y - r).abs().max()) / max(rms, 1e-30)
+
+
+# ---------------------------------------------------------------------------
+# Embedding lookups
+# ---------------------------------------------------------------------------
+
+
+def vq_embedding(input_ids: torch.Tensor, all_indices: torch.Tensor, centroids: torch.Tensor,
+                 embedding_dim: int, scale: float = 1.0, inv_perm: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``NPVQEmbedding.forward`` (neuropress/nn/np_vq_embedding.py:119-141): gather the 16-bit
+    index rows, gather fp16 centroids, reshape, optional column permutation, optional multiply by
+    a python scalar (fp16 result), optional cast."""
+    flat = input_ids.detach().cpu().flatten()
+    idx = all_indices.detach().cpu().to(torch.int16)[flat].long()
+    out = centroids.detach().cpu().to(torch.float16)[idx].reshape(flat.shape[0], embedding_dim)
+    if inv_perm is not None:
+        out = out[:, inv_perm.detach().cpu()]
+    if scale != 1.0:
+        out = out * scale
+    if out_dtype is not None:
+        out = out.to(out_dtype)
+    return out.reshape(*input_ids.shape, embedding_dim)
+
+
+def q_embedding(input_ids: torch.Tensor, u8_blob, scale: torch.Tensor, nbits: int, group_size: int,
+                zero_point: torch.Tensor | None = None, padding_idx: int | None = None,
+                embed_scale: float = 1.0, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``_emb_dequant`` followed by the tail of ``NPEmbedding.forward``
+    (neuropress/nn/np_embedding.py:120-183, 449-473, 497-503): gather packed rows, unpack,
+    ``((q - zp) * s)`` in fp32, cast to the fp16 scale dtype, zero the padding rows, cast to
+    ``out_dtype``, multiply by ``embed_scale``."""
+    blob = torch.from_numpy(_as_np_u8(u8_blob))
+    ids = input_ids.detach().cpu()
+    flat = ids.reshape(-1)
+    n_emb = blob.shape[0]
+    dim = blob.shape[1] * (8 // nbits)
+    ng = dim // group_size
+    vals = torch.from_numpy(unpack_codes(blob[flat].numpy(), nbits).astype(np.float32)).reshape(-1, ng, group_size)
+    sc16 = scale.detach().cpu().to(torch.float16)
+    sc = sc16.reshape(n_emb, ng)[flat].to(torch.float32).unsqueeze(-1)
+    if zero_point is not None:
+        zp = zero_point.detach().cpu().reshape(n_emb, ng)[flat].to(torch.float32).unsqueeze(-1)
+        out = (vals - zp) * sc
+    else:
+        out = (vals - float(1 << (nbits - 1))) * sc
+    out = out.reshape(-1, dim).to(sc16.dtype).reshape(*ids.shape, dim)
+    if padding_idx is not None:
+        out = out.clone()
+        out[ids == padding_idx] = 0.0
+    if out_dtype is not None:
+        out = out.to(out_dtype)
+    if embed_scale != 1.0:
+        out = out * embed_scale
+    return out
 
 
 # ---------------------------------------------------------------------------

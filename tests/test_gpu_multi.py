@@ -81,6 +81,22 @@ def _worker(rank: int, world: int, port: int, q) -> None:
             assert_output_close(y, refs[rows][1], torch.bfloat16)
         assert layer.push.status() == 0
 
+        # outside what the peer-store buffers were built for (more rows than max_rows, another
+        # dtype): the layer falls back to the NCCL all-gather instead of raising
+        xb = make_activations(400, 1024, torch.bfloat16, seed=400)
+        yb = layer(xb.to(dev))
+        assert yb.shape == (400, 512)
+        assert_output_close(yb, oracle.vq_forward_f32(xb, d.packed, d.centroids, 16, 512, 1024, d.bias, **d.ext()),
+                            torch.bfloat16)
+        xf = make_activations(2, 1024, torch.float32, seed=7)
+        yf = layer(xf.to(dev))
+        assert yf.shape == (2, 512) and yf.dtype == torch.float32
+        assert_output_close(yf, oracle.vq_forward_f32(xf, d.packed, d.centroids, 16, 512, 1024, d.bias, **d.ext()),
+                            torch.float32)
+        y2 = layer(refs[2][0])                        # and back inside the envelope
+        assert_output_close(y2, refs[2][1], torch.bfloat16)
+        assert layer.push.status() == 0
+
         # a group-affine (HQQ-style) layer through the same fused all-gather
         from neuropress_b200.nn import NPLinear
         from synthetic import make_q_layer
