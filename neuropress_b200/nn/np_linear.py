@@ -159,8 +159,9 @@ class NPLinear(nn.Module):
         from ..qtensor import AffineQTensor, AffineScheme
 
         scheme = AffineScheme(self.nbits, self.group_size, self.scale, self.zero_point)
+        meta = {k: v for k, v in self._qtensor_meta.items() if k not in ("type", "shape")}
         return AffineQTensor(self.u8_blob, scheme, (self.out_features, self.in_features),
-                             self._compute_dtype, dict(self._qtensor_meta))
+                             self._compute_dtype, meta)
 
     def set_backend(self, backend: str | LinearBackend | None) -> "NPLinear":
         """Switch backend in place (reference :651-700)."""

@@ -284,9 +284,11 @@ class NPVQLinear(nn.Module):
         from ..qtensor import VQQTensor, VQScheme
 
         scheme = VQScheme(centroids=self.proxy.centroids, vector_len=self.vector_len,
-                          is_packed_indices=self.bits, column_permutation=self.column_perm)
+                          is_packed_indices=self.bits, column_permutation=self.column_perm,
+                          original_shape=(self.out_features, self.in_features))
+        meta = {k: v for k, v in self._qtensor_meta.items() if k not in ("type", "shape")}
         return VQQTensor(u8_blob=self.packed_indices, qscheme=scheme,
-                         shape=(self.out_features, self.in_features), meta=dict(self._qtensor_meta))
+                         shape=(self.out_features, self.in_features), meta=meta)
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, gather=None) -> torch.Tensor:

@@ -40,8 +40,18 @@ class VQQTensor:
     shape: tuple[int, int]
     meta: dict = field(default_factory=dict)
 
+    dequant_to_dtype: torch.dtype | None = None
+
+    def __post_init__(self) -> None:
+        if self.dequant_to_dtype is None:
+            self.dequant_to_dtype = getattr(torch, self.meta.get("dequant_to_dtype", "float16"))
+        else:
+            self.meta.setdefault("dequant_to_dtype", str(self.dequant_to_dtype).replace("torch.", ""))
+
     def serde_metadata(self) -> dict:
-        return {"type": "QTensorTractVQ", "shape": list(self.shape), **self.meta}
+        """What a lowered module keeps to rebuild this weight: the checkpoint fields that are not
+        buffers of the module (plus type and shape, for inspection)."""
+        return {"type": "QTensorTractVQ", "shape": list(self.shape) if self.shape else None, **self.meta}
 
 
 @dataclass(eq=False)
