@@ -970,41 +970,49 @@ def run_c4(device, peaks, layers_n: int = 16, bits: int = 16) -> dict:
         torch.cuda.current_stream().wait_stream(side)
         return t0.elapsed_time(t1) / reps
 
-    with torch.no_grad():
-        for batch in (1, 8, 64):
-            cache = StaticCache(config=cfg, max_cache_len=ctx + 32)
-            prompt = device_normal((batch, ctx, 2048), device, 11 + batch)
-            model(inputs_embeds=prompt, past_key_values=cache, use_cache=True,
-                  cache_position=torch.arange(ctx, device=device))
-            tok = device_normal((batch, 1, 2048), device, 12 + batch)
-            pos = torch.tensor([ctx], device=device)
+    def measure(tag: str) -> None:
+        with torch.no_grad():
+            for batch in (1, 8, 64):
+                cache = StaticCache(config=cfg, max_cache_len=ctx + 32)
+                prompt = device_normal((batch, ctx, 2048), device, 11 + batch)
+                model(inputs_embeds=prompt, past_key_values=cache, use_cache=True,
+                      cache_position=torch.arange(ctx, device=device))
+                tok = device_normal((batch, 1, 2048), device, 12 + batch)
+                pos = torch.tensor([ctx], device=device)
 
-            def step(tok=tok, cache=cache, pos=pos):
-                return model(inputs_embeds=tok, past_key_values=cache, use_cache=True, cache_position=pos)
-            try:
-                ms = timed_graph(step)
-                how = "CUDA-graph replay"
-            except Exception as exc:
-                torch.cuda.synchronize()
-                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                for _ in range(2):
-                    step()
-                t0.record()
-                for _ in range(5):
-                    step()
-                t1.record()
-                torch.cuda.synchronize()
-                ms = t0.elapsed_time(t1) / 5
-                how = f"eager ({type(exc).__name__} during capture)"
-            out[f"decode_batch{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / (ms * 1e-3), 1),
-                                           "launch": how}
-        x = device_normal((1, 512, 2048), device, 99)
+                def step(tok=tok, cache=cache, pos=pos):
+                    return model(inputs_embeds=tok, past_key_values=cache, use_cache=True, cache_position=pos)
+                try:
+                    ms = timed_graph(step)
+                    how = "CUDA-graph replay"
+                except Exception as exc:
+                    torch.cuda.synchronize()
+                    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    for _ in range(2):
+                        step()
+                    t0.record()
+                    for _ in range(5):
+                        step()
+                    t1.record()
+                    torch.cuda.synchronize()
+                    ms = t0.elapsed_time(t1) / 5
+                    how = f"eager ({type(exc).__name__} during capture)"
+                out[f"decode_batch{batch}{tag}"] = {"ms_per_step": round(ms, 4),
+                                                    "tokens_per_s": round(batch / (ms * 1e-3), 1), "launch": how}
+            x = device_normal((1, 512, 2048), device, 99)
 
-        def prefill():
-            return model(inputs_embeds=x, use_cache=False)
-        ms = timed_graph(prefill, reps=3)
-        out["prefill512"] = {"ms": round(ms, 4), "tokens_per_s": round(512 / (ms * 1e-3), 1),
-                             "TFLOPs_linears": round(2.0 * 512 * (index_bytes // 2 * 8) / (ms * 1e-3) / 1e12, 1)}
+            def prefill():
+                return model(inputs_embeds=x, use_cache=False)
+            ms = timed_graph(prefill, reps=3)
+            out[f"prefill512{tag}"] = {"ms": round(ms, 4), "tokens_per_s": round(512 / (ms * 1e-3), 1),
+                                       "TFLOPs_linears": round(2.0 * 512 * (index_bytes // 2 * 8) / (ms * 1e-3) / 1e12, 1)}
+
+    measure("_one_launch_per_module")
+    # q / k / v and gate / up as one launch each, the norm in front of them folded in
+    from neuropress_b200.nn import group_shared_input_linears
+
+    out["groups_made"] = group_shared_input_linears(model)
+    measure("")
     b1 = out.get("decode_batch1")
     if b1:
         out["frac_of_hbm_ceiling_batch1"] = round(b1["tokens_per_s"] / out["hbm_ceiling_tok_s_batch1"], 4)

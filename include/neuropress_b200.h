@@ -111,6 +111,22 @@ int npb_q_decode(const npb_q_weight* w, int64_t N, int64_t K, void* out, int out
 int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,
                 int64_t K, const float* bias, void* y, npb_stream_t stream);
 
+/* Grouped launch: n_weights (1..4) weights that are applied to the SAME activations -- the q / k / v
+ * or the gate / up projections of a decoder layer -- in one kernel, as if their rows were
+ * stacked: y is [M, sum N_i] with weight i at columns [sum_{j<i} N_j, +N_i).  Ns and biases are
+ * HOST arrays (biases NULL, or device pointers / NULL per weight).  Optionally the activations
+ * are RMS-normalised on their way into shared memory: norm_weight [K] in x_dtype (NULL: none),
+ * x' = T(x * rsqrt(mean(x^2) + norm_eps) * norm_weight) in fp32, the arithmetic of npb_rms_norm, so
+ * the norm before q / k / v or gate / up costs no launch and no HBM round trip.  1..16 rows, the
+ * weight forms of the tensor-core path of npb_vq_gemv without residual codebook / row scale, all
+ * weights with the same index width and codebook layout; otherwise NPB_ERR_UNSUPPORTED (call
+ * npb_rms_norm and npb_vq_gemv per weight instead).  No reference counterpart: the reference
+ * launches one kernel per linear and one per norm (neuropress/nn/np_vq_linear.py:1250-1267,
+ * neuropress/nn/np_rms_norm.py:86-99). */
+int npb_vq_gemv_grouped(const npb_vq_weight* weights, int n_weights, const int64_t* Ns,
+                        const float* const* biases, const void* x, int x_dtype, int64_t M, int64_t K,
+                        const void* norm_weight, float norm_eps, void* y, npb_stream_t stream);
+
 /* Same contract for group-affine weights.  Replaces q_linear
  * (neuropress/kernels/q4_linear.cu:179-253). */
 int npb_q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,

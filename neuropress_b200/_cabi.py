@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "npb_q_decode",
     "npb_vq_gemv",
     "npb_q_gemv",
+    "npb_vq_gemv_grouped",
     "npb_gemm",
     "npb_vq_gemm_fused",
     "npb_q_gemm_fused",
@@ -127,6 +128,8 @@ def load_library() -> ctypes.CDLL:
     gemv_tail = [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p]
     lib.npb_vq_gemv.argtypes = [vq_p, *gemv_tail]
     lib.npb_q_gemv.argtypes = [q_p, *gemv_tail]
+    lib.npb_vq_gemv_grouped.argtypes = [vq_p, c_int, POINTER(c_int64), POINTER(c_void_p), c_void_p, c_int, c_int64,
+                                        c_int64, c_void_p, ctypes.c_float, c_void_p, c_void_p]
     lib.npb_vq_gemm_fused.argtypes = [vq_p, *gemv_tail]
     lib.npb_vq_linear_static_scratch.argtypes = [vq_p, *gemv_tail]
     lib.npb_q_gemm_fused.argtypes = [q_p, *gemv_tail]

@@ -31,6 +31,8 @@ int gemm_device_status(int*);
 int vq_gemv_mma(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
                 const GatherSink*, cudaStream_t);
 int rms_norm(const void*, const void*, void*, int64_t, int64_t, float, int, cudaStream_t);
+int vq_gemv_grouped(const npb_vq_weight*, int, const int64_t*, const float* const*, const void*, int, int64_t,
+                    int64_t, const void*, float, void*, cudaStream_t);
 int vq_embedding(const int64_t*, int64_t, const uint16_t*, int64_t, int64_t, const void*, int, int, const int64_t*,
                  float, void*, int, cudaStream_t);
 int q_embedding(const int64_t*, int64_t, const npb_q_weight*, int64_t, int64_t, int64_t, float, void*, int,
@@ -188,6 +190,13 @@ int npb_vq_gemv(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, i
     if (rc != NPB_ERR_UNSUPPORTED) return rc;
   }
   return npb::vq_gemv(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_gemv_grouped(const npb_vq_weight* weights, int n_weights, const int64_t* Ns,
+                        const float* const* biases, const void* x, int x_dtype, int64_t M, int64_t K,
+                        const void* norm_weight, float norm_eps, void* y, npb_stream_t stream) {
+  return npb::vq_gemv_grouped(weights, n_weights, Ns, biases, x, x_dtype, M, K, norm_weight, norm_eps, y,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int npb_q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,

@@ -30,6 +30,18 @@
 namespace npb {
 namespace {
 
+// One weight of a grouped launch: several weights that share the activations (q / k / v, or
+// gate / up) are walked by one kernel as if their rows were stacked.
+struct MmaSeg {
+  const uint8_t* packed;
+  const __half* centroids;
+  const float* bias;
+  int N;        // rows of this weight
+  int group0;   // first 16-row group of this weight in the stacked order
+  int col0;     // first output column
+};
+constexpr int kMaxSegs = 4;
+
 struct MmaVqArgs {
   const uint8_t* packed;
   const __half* centroids;
@@ -44,6 +56,13 @@ struct MmaVqArgs {
   int M, N, K, G;
   int slices_per_warp;
   GatherSink sink;  // peer_out != null: y goes to this rank's own [M, ld] buffer, then the tail
+  // grouped launch (n_segs > 1): the per-weight fields above are unused; no residual / row scale
+  int n_segs, ld_y, total_groups;
+  MmaSeg seg[kMaxSegs];
+  // fused RMSNorm of the activations while they are staged (norm_w == null: none):
+  // x' = T(x * rsqrt(mean(x^2) + eps) * norm_w), fp32 arithmetic, rounded once like the norm kernel
+  const void* norm_w;
+  float norm_eps;
 };
 
 // fp16 pair -> the activation type, one rounding (bf16 through fp32, as from_half<bf16>).
@@ -122,10 +141,37 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   {
     const T* x = static_cast<const T*>(a.x);
     const int chunks = K / 8;
+    float* inv_rms = part;  // [MT * 8], reused as the partial-sum area after the barrier below
+    if (a.norm_w != nullptr) {
+      for (int m = warp; m < a.M; m += WARPS) {  // one warp per activation row
+        float ss = 0.f;
+        for (int c = lane; c < chunks; c += 32) {
+          const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + c * 8);
+          const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const float f = to_f32(e[j]); ss = fmaf(f, f, ss); }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) inv_rms[m] = rsqrtf(ss / (float)K + a.norm_eps);
+      }
+      __syncthreads();
+    }
     for (int i = tid; i < MT * 8 * chunks; i += WARPS * 32) {
       const int m = i / chunks, c = i - m * chunks;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (m < a.M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + c * 8);
+      if (m < a.M) {
+        v = *reinterpret_cast<const uint4*>(x + (size_t)m * K + c * 8);
+        if (a.norm_w != nullptr) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.norm_w) + c * 8);
+          const T* e = reinterpret_cast<const T*>(&v);
+          const T* we = reinterpret_cast<const T*>(&wv);
+          struct alignas(16) Out { T o[8]; } r;
+          const float inv = inv_rms[m];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r.o[j] = from_f32<T>(to_f32(e[j]) * inv * to_f32(we[j]));
+          v = *reinterpret_cast<const uint4*>(&r);
+        }
+      }
       const int phys = (c & ~31) | xchunk(c & 31);
       *reinterpret_cast<uint4*>(xs + (size_t)m * xstride + phys * 16) = v;
     }
@@ -137,18 +183,30 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   }
   __syncthreads();
 
-  const int n_groups = (a.N + 15) / 16;
+  const int n_groups = a.n_segs > 1 ? a.total_groups : (a.N + 15) / 16;
   const int chunks_per_row = a.G >> 3;  // 8-index chunks per W row
+  // Weight that owns row group rg: its index stream, codebook, row count and first group.
+  struct SegView { const uint8_t* packed; const __half* centroids; const float* bias; int N, group0, col0; };
+  auto seg_of = [&](int rg_) -> SegView {
+    if (a.n_segs <= 1) return SegView{a.packed, a.centroids, a.bias, a.N, 0, 0};
+    int s_ = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxSegs; ++i)
+      if (i < a.n_segs && rg_ >= a.seg[i].group0) s_ = i;
+    return SegView{a.seg[s_].packed, a.seg[s_].centroids, a.seg[s_].bias, a.seg[s_].N, a.seg[s_].group0,
+                   a.seg[s_].col0};
+  };
   const bool has_res = a.has_res != 0, has_scale = a.has_scale != 0;
   // Index words of one (row group, slice) item for this lane's two rows; the next item's are
   // requested before the current item's gathers, so their latency is off the critical path.
   struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; };
   auto fetch = [&](Item& it, int rg_, int sl_) {
-    const int nl = rg_ * 16 + g, nh = nl + 8;
-    const int rl = nl < a.N ? nl : a.N - 1, rh = nh < a.N ? nh : a.N - 1;  // rows past N: row N-1
+    const SegView sv = seg_of(rg_);
+    const int nl = (rg_ - sv.group0) * 16 + g, nh = nl + 8;
+    const int rl = nl < sv.N ? nl : sv.N - 1, rh = nh < sv.N ? nh : sv.N - 1;  // rows past N: row N-1
     const int c0 = (warp * a.slices_per_warp + sl_) * 4 + t;               // chunk of 8 indices in the row
-    it.lo = load_raw<BITS>(a.packed, (int64_t)rl * chunks_per_row + c0);
-    it.hi = load_raw<BITS>(a.packed, (int64_t)rh * chunks_per_row + c0);
+    it.lo = load_raw<BITS>(sv.packed, (int64_t)rl * chunks_per_row + c0);
+    it.hi = load_raw<BITS>(sv.packed, (int64_t)rh * chunks_per_row + c0);
     if (has_res) {
       it.rlo = load_raw<8>(a.res_packed, (int64_t)rl * chunks_per_row + c0);
       it.rhi = load_raw<8>(a.res_packed, (int64_t)rh * chunks_per_row + c0);
@@ -160,9 +218,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   if ((int)blockIdx.x < n_groups) fetch(nxt, blockIdx.x, 0);
   int buf = 0;
   for (int rg = blockIdx.x; rg < n_groups; rg += gridDim.x, buf ^= 1) {
-    const int n_lo = rg * 16 + g, n_hi = n_lo + 8;
+    const SegView sv = seg_of(rg);
+    const int n_lo = (rg - sv.group0) * 16 + g, n_hi = n_lo + 8;
     // rows past N read row N - 1 (mapped); their results are not stored
-    const int r_lo = n_lo < a.N ? n_lo : a.N - 1, r_hi = n_hi < a.N ? n_hi : a.N - 1;
+    const int r_lo = n_lo < sv.N ? n_lo : sv.N - 1, r_hi = n_hi < sv.N ? n_hi : sv.N - 1;
     __half2 s_lo = __float2half2_rn(1.f), s_hi = s_lo;
     if (has_scale) {
       s_lo = __half2half2(__ldg(a.row_scale + (has_scale ? r_lo : 0)));
@@ -195,8 +254,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
         Half8 c_lo[4], c_hi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(a.centroids) + idx_lo[4 * h + j]);
-          c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(a.centroids) + idx_hi[4 * h + j]);
+          c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_lo[4 * h + j]);
+          c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_hi[4 * h + j]);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -249,12 +308,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
 #pragma unroll 4
       for (int w = 0; w < WARPS; ++w) sum += p[(size_t)w * MT * 128];
       const int mt = i >> 7, ln = (i >> 2) & 31, c = i & 3;
-      const int n = rg * 16 + (ln >> 2) + 8 * (c >> 1);
+      const int n = (rg - sv.group0) * 16 + (ln >> 2) + 8 * (c >> 1);
       const int m = mt * 8 + 2 * (ln & 3) + (c & 1);
-      if (n < a.N && m < a.M) {
-        if (a.bias) sum += __ldg(a.bias + n);
+      if (n < sv.N && m < a.M) {
+        if (sv.bias) sum += __ldg(sv.bias + n);
         if (a.sink.peer_out == nullptr)
-          static_cast<T*>(a.y)[(size_t)m * a.N + n] = from_f32<T>(sum);
+          static_cast<T*>(a.y)[(size_t)m * a.ld_y + sv.col0 + n] = from_f32<T>(sum);
         else
           static_cast<T*>(a.sink.peer_out[a.sink.rank])[(size_t)m * a.sink.ld + a.sink.col0 + n] =
               from_f32<T>(sum);
@@ -275,7 +334,7 @@ int launch(const MmaVqArgs& a, cudaStream_t st) {
   int per_sm = 0;
   if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), WARPS * 32, smem, &per_sm)) return rc;
   if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
-  const int n_groups = (a.N + 15) / 16;
+  const int n_groups = a.n_segs > 1 ? a.total_groups : (a.N + 15) / 16;
   const int cap = sm_count() * per_sm;
   kern<<<n_groups < cap ? n_groups : cap, WARPS * 32, smem, st>>>(a);
   NPB_LAUNCH_CHECK();
@@ -339,9 +398,70 @@ int vq_gemv_mma(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, i
   a.res_num_centroids = a.has_res ? w->res_num_centroids : 0;
   a.groups_per_codebook = gpc;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.G = (int)(K / 8);
+  a.n_segs = 1;
+  a.ld_y = (int)N;
   if (sink) a.sink = *sink;
   return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(a, w->bits, st)
                              : launch_bits<__half>(a, w->bits, st);
+}
+
+// Grouped launch: n_w weights of the same K / index width / codebook layout applied to the same
+// activations in ONE kernel; y is [M, sum of N_i] with weight i at columns [sum_{j<i} N_j, +N_i).
+// Optionally the activations are RMS-normalised while they are staged (norm_w != null).  Plain
+// weights only (no residual codebook, no row scale); NPB_ERR_UNSUPPORTED for anything the
+// tensor-core small-batch kernel does not take.
+int vq_gemv_grouped(const npb_vq_weight* ws, int n_w, const int64_t* Ns, const float* const* biases,
+                    const void* x, int x_dtype, int64_t M, int64_t K, const void* norm_w, float norm_eps,
+                    void* y, cudaStream_t st) {
+  if (ws == nullptr || Ns == nullptr || n_w < 1 || n_w > kMaxSegs) return NPB_ERR_INVALID_ARG;
+  if (x_dtype != NPB_BF16 && x_dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
+  if (M < 1 || M > 16 || K % 1024 != 0 || K > 16384) return NPB_ERR_UNSUPPORTED;
+  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (!aligned_to(x, 16) || (norm_w && !aligned_to(norm_w, 16))) return NPB_ERR_UNSUPPORTED;
+  MmaVqArgs a{};
+  int64_t total_n = 0, groups = 0;
+  for (int i = 0; i < n_w; ++i) {
+    const npb_vq_weight* w = ws + i;
+    if (int rc = validate_vq(w, Ns[i], K)) return rc;
+    if (Ns[i] < 1) return NPB_ERR_INVALID_ARG;
+    if (w->vector_len != 8 || w->bits != ws[0].bits || (w->bits != 16 && w->bits != 12 && w->bits != 8))
+      return NPB_ERR_UNSUPPORTED;
+    if (w->res_packed != nullptr || w->row_scale != nullptr) return NPB_ERR_UNSUPPORTED;
+    if (w->cols_per_codebook != ws[0].cols_per_codebook || w->num_centroids != ws[0].num_centroids)
+      return NPB_ERR_UNSUPPORTED;
+    if (!aligned_to(w->packed, index8_alignment(w->bits)) || !aligned_to(w->centroids, 16)) return NPB_ERR_UNSUPPORTED;
+    a.seg[i].packed = w->packed;
+    a.seg[i].centroids = static_cast<const __half*>(w->centroids);
+    a.seg[i].bias = biases ? biases[i] : nullptr;
+    a.seg[i].N = (int)Ns[i];
+    a.seg[i].group0 = (int)groups;
+    a.seg[i].col0 = (int)total_n;
+    groups += (Ns[i] + 15) / 16;
+    total_n += Ns[i];
+  }
+  if (total_n >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
+  const int gpc = ws[0].cols_per_codebook > 0 ? ws[0].cols_per_codebook / 8 : 0;
+  if (gpc % 32 != 0) return NPB_ERR_UNSUPPORTED;
+  // single-weight fields: alias the first weight so that every pointer the kernel can form is mapped
+  a.packed = ws[0].packed;
+  a.centroids = a.seg[0].centroids;
+  a.res_packed = a.packed;
+  a.res_centroids = a.centroids;
+  a.row_scale = a.centroids;
+  a.bias = nullptr;
+  a.x = x;
+  a.y = y;
+  a.num_centroids = ws[0].num_centroids;
+  a.groups_per_codebook = gpc;
+  a.M = (int)M; a.N = (int)Ns[0]; a.K = (int)K; a.G = (int)(K / 8);
+  a.n_segs = n_w == 1 ? 1 : n_w;
+  if (n_w == 1) { a.bias = a.seg[0].bias; }
+  a.ld_y = (int)total_n;
+  a.total_groups = (int)groups;
+  a.norm_w = norm_w;
+  a.norm_eps = norm_eps;
+  return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(a, ws[0].bits, st)
+                             : launch_bits<__half>(a, ws[0].bits, st);
 }
 
 }  // namespace npb

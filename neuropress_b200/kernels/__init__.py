@@ -165,6 +165,39 @@ def vq_gemv(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tens
     return _vq_call("npb_vq_gemv", x, packed_indices, centroids, bits, out_features, bias, ext, gather)
 
 
+def vq_gemv_grouped(x: torch.Tensor, weights: list[tuple], bits: int, cols_per_codebook: int = 0,
+                    norm_weight: torch.Tensor | None = None, norm_eps: float = 1e-6) -> torch.Tensor | None:
+    """Several VQ weights applied to the same ``x`` ``[M, K]`` (M <= 16) in ONE launch, optionally
+    with the RMSNorm of ``x`` fused into its staging.  ``weights`` is a list of ``(packed_indices,
+    centroids, out_features, bias_f32_or_None)``; returns ``[M, sum(out_features)]`` with the
+    weights' outputs side by side -- or ``None`` when the kernel does not take this combination
+    (the caller then runs the norm and the linears one by one)."""
+    if x.dim() != 2 or not 1 <= len(weights) <= 4:
+        return None
+    _cabi.require_cuda("vq_gemv_grouped", x, norm_weight, *[t for w in weights for t in (w[0], w[1], w[3])])
+    lib = _cabi.load_library()
+    m, k = x.shape
+    n_w = len(weights)
+    structs = (_cabi.VQWeightStruct * n_w)()
+    ns = (ctypes.c_int64 * n_w)()
+    biases = (ctypes.c_void_p * n_w)()
+    for i, (packed, cent, n, bias) in enumerate(weights):
+        structs[i] = _cabi.vq_struct(packed, cent, bits, cols_per_codebook=cols_per_codebook)
+        ns[i] = int(n)
+        biases[i] = None if bias is None else bias.data_ptr()
+    if norm_weight is not None and (norm_weight.dtype != x.dtype or norm_weight.numel() != k):
+        raise RuntimeError("vq_gemv_grouped: norm_weight must be [K] in the activation dtype.")
+    y = torch.empty((m, sum(int(w[2]) for w in weights)), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _launch("npb_vq_gemv_grouped", lib.npb_vq_gemv_grouped, structs, n_w, ns, biases, x.data_ptr(),
+                     _cabi.dtype_code(x.dtype), m, k, None if norm_weight is None else norm_weight.data_ptr(),
+                     float(norm_eps), y.data_ptr(), _cabi.stream_ptr())
+    if rc == 2:   # NPB_ERR_UNSUPPORTED: not a combination the grouped kernel takes
+        return None
+    _cabi.check(rc, "vq_gemv_grouped")
+    return y
+
+
 def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
                   bits: int, out_features: int | None = None, bias: torch.Tensor | None = None,
                   **ext) -> torch.Tensor:
