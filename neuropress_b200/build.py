@@ -32,6 +32,7 @@ SOURCES = [
     "vq_gemv.cu",
     "q_kernels.cu",
     "q_gemv_mma.cu",
+    "q_gemv_ring.cu",
     "gemm_tcgen05.cu",
     "vq_gemm_fused.cu",
     "static_scratch.cu",

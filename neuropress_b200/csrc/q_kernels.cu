@@ -20,6 +20,8 @@
 
 namespace npb {
 
+int q4_gemv_ring(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, const float*, void*,
+                 cudaStream_t);
 int q4_gemv_mma(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
                 void*, cudaStream_t);
 
@@ -454,6 +456,11 @@ int q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t
   a.x = x;
   a.y = y;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.group_size = w->group_size;
+  if (M <= 2) {
+    // 1-2 rows: the weight streamed through a shared-memory ring by bulk async copies
+    const int rc = q4_gemv_ring(w, x, x_dtype, M, N, K, bias, y, st);
+    if (rc != NPB_ERR_UNSUPPORTED) return rc;
+  }
   {
     // Tensor-core GEMV first (bf16 / fp16, K % 512 == 0); it declines other shapes.
     const int rc = q4_gemv_mma(w, x, x_dtype, M, N, K, bias, y, st);

@@ -172,6 +172,25 @@ def test_q_gemv_matches_oracle(asym, gs, dtype, rows, shape):
     assert_output_close(y, ref, dtype)
 
 
+@pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows", [1, 2])
+@pytest.mark.parametrize("shape", [(67, 4096), (1192, 4096), (200, 8192), (2411, 4096)])
+def test_q_gemv_ring_shapes(asym, gs, dtype, rows, shape):
+    """K a multiple of 4096 and 1-2 rows take the bulk-copy ring GEMV: row counts that are not
+    multiples of 8 (the last ring stage re-reads the last row), several stages per CTA, two step
+    pairs per warp (K = 8192)."""
+    N, K = shape
+    layer = make_q_layer(N, K, group_size=gs, asym=asym, seed=N + gs, bias=True)
+    x = make_activations(rows, K, dtype, seed=rows + N)
+    y = kernels.q_gemv(x.to(DEV), layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                       None if layer.zero_point is None else layer.zero_point.to(DEV), layer.bias.to(DEV))
+    ref = oracle.q_forward_f64(x, layer.codes, layer.scale, 4, gs, layer.zero_point, layer.bias)
+    assert_output_close(y, ref, dtype)
+    from neuropress_b200 import _cabi
+    assert _cabi.gemm_device_status() == 0
+
+
 # ------------------------------------------------------------------- dense tcgen05 GEMM ---
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 512), (256, 512, 1024),
                                    (130, 72, 96), (1, 64, 64), (2048, 1024, 512), (300, 14336, 256)])
