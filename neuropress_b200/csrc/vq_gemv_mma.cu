@@ -58,6 +58,7 @@ struct MmaVqArgs {
   GatherSink sink;  // peer_out != null: y goes to this rank's own [M, ld] buffer, then the tail
   // grouped launch (n_segs > 1): the per-weight fields above are unused; no residual / row scale
   int n_segs, ld_y, total_groups;
+  int cb_entries;  // codebook entries over all column blocks (shared-memory staging)
   MmaSeg seg[kMaxSegs];
   // fused RMSNorm of the activations while they are staged (norm_w == null: none):
   // x' = T(x * rsqrt(mean(x^2) + eps) * norm_w), fp32 arithmetic, rounded once like the norm kernel
@@ -124,7 +125,7 @@ __device__ __forceinline__ void expand(const RawIdx<BITS>& r, uint32_t (&idx)[8]
 // four different bank groups.
 __device__ __forceinline__ int xchunk(int c) { return c ^ ((c >> 3) & 3); }
 
-template <typename T, int BITS, int MT, int WARPS>
+template <typename T, int BITS, int MT, int WARPS, bool CBS>
 __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -136,6 +137,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   uint8_t* xs = smem;
   float* part = reinterpret_cast<float*>(smem + (size_t)MT * 8 * xstride);  // [2][WARPS][MT][32][4]
   uint4* rtab = reinterpret_cast<uint4*>(part + 2 * WARPS * MT * 128);      // residual table x 8
+  // CBS: the whole codebook (all column blocks) staged in shared memory -- a gather from there
+  // costs a bank-conflicted LDS instead of one L1 tag lookup per lane (1 per clock per SM)
+  const uint4* cbs = rtab + (a.has_res ? a.res_num_centroids * 8 : 0);
 
   // ---- stage activations (zero rows past M) and the replicated residual table ----
   {
@@ -179,6 +183,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
       // entry e at slots 8 e .. 8 e + 7; a lane reads slot 8 e + (lane & 7): conflict-free
       for (int i = tid; i < a.res_num_centroids * 8; i += WARPS * 32)
         rtab[i] = __ldg(reinterpret_cast<const uint4*>(a.res_centroids) + (i >> 3));
+    }
+    if constexpr (CBS) {
+      uint4* dst = const_cast<uint4*>(cbs);
+      for (int i = tid; i < a.cb_entries; i += WARPS * 32)
+        dst[i] = __ldg(reinterpret_cast<const uint4*>(a.centroids) + i);
     }
   }
   __syncthreads();
@@ -254,8 +263,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
         Half8 c_lo[4], c_hi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_lo[4 * h + j]);
-          c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_hi[4 * h + j]);
+          if constexpr (CBS) {
+            c_lo[j] = *reinterpret_cast<const Half8*>(cbs + idx_lo[4 * h + j]);
+            c_hi[j] = *reinterpret_cast<const Half8*>(cbs + idx_hi[4 * h + j]);
+          } else {
+            c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_lo[4 * h + j]);
+            c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_hi[4 * h + j]);
+          }
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -325,12 +339,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   if (a.sink.peer_out != nullptr) gather_tail_small<T>(a.sink, a.M, a.N);
 }
 
-template <typename T, int BITS, int MT, int WARPS>
-int launch(const MmaVqArgs& a, cudaStream_t st) {
-  const size_t xbytes = (size_t)MT * 8 * ((size_t)a.K * sizeof(T) + 64);
-  const size_t smem = xbytes + (size_t)2 * WARPS * MT * 128 * 4 + (a.has_res ? 256 * 8 * 16 : 0);
-  if (smem > (size_t)max_dynamic_smem()) return NPB_ERR_UNSUPPORTED;
-  auto kern = vq_gemv_mma_kernel<T, BITS, MT, WARPS>;
+template <typename T, int BITS, int MT, int WARPS, bool CBS>
+int launch_cb(const MmaVqArgs& a, size_t smem, cudaStream_t st) {
+  auto kern = vq_gemv_mma_kernel<T, BITS, MT, WARPS, CBS>;
   int per_sm = 0;
   if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), WARPS * 32, smem, &per_sm)) return rc;
   if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
@@ -339,6 +350,23 @@ int launch(const MmaVqArgs& a, cudaStream_t st) {
   kern<<<n_groups < cap ? n_groups : cap, WARPS * 32, smem, st>>>(a);
   NPB_LAUNCH_CHECK();
   return NPB_OK;
+}
+
+template <typename T, int BITS, int MT, int WARPS>
+int launch(const MmaVqArgs& a, cudaStream_t st) {
+  const size_t xbytes = (size_t)MT * 8 * ((size_t)a.K * sizeof(T) + 64);
+  const size_t smem = xbytes + (size_t)2 * WARPS * MT * 128 * 4 + (a.has_res ? 256 * 8 * 16 : 0);
+  const size_t cap = (size_t)max_dynamic_smem();
+  if (smem > cap) return NPB_ERR_UNSUPPORTED;
+  // Codebook in shared memory when it fits beside the activations and every CTA gathers several
+  // times more vectors than the staging copies (one weight only: each has its own codebook).
+  const size_t cb_bytes = (size_t)a.cb_entries * 16;
+  const int n_groups = (a.N + 15) / 16;
+  const int64_t ctas = n_groups < sm_count() ? n_groups : sm_count();
+  const int64_t gathers_per_cta = (int64_t)(n_groups + ctas - 1) / ctas * 16 * a.G;
+  if (a.n_segs <= 1 && a.cb_entries > 0 && smem + cb_bytes <= cap && gathers_per_cta >= 3 * (int64_t)a.cb_entries)
+    return launch_cb<T, BITS, MT, WARPS, true>(a, smem + cb_bytes, st);
+  return launch_cb<T, BITS, MT, WARPS, false>(a, smem, st);
 }
 
 template <typename T, int BITS, int MT>
@@ -400,6 +428,8 @@ int vq_gemv_mma(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, i
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.G = (int)(K / 8);
   a.n_segs = 1;
   a.ld_y = (int)N;
+  a.cb_entries = w->num_centroids * (w->cols_per_codebook > 0
+                                         ? (int)((K + w->cols_per_codebook - 1) / w->cols_per_codebook) : 1);
   if (sink) a.sink = *sink;
   return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(a, w->bits, st)
                              : launch_bits<__half>(a, w->bits, st);
