@@ -611,6 +611,12 @@ def run_ours(args) -> dict:
     return line if rank == 0 else {}
 
 
+# DRAM bytes (read + write) of single launches on the unsharded gate projection at 4096 rows, from one
+# `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum` capture of `--case c5:gate:4096`.
+NCU_GATE_GEMM_DRAM_BYTES = 1401767168 + 224070144
+NCU_GATE_DECODE_DRAM_BYTES = 59784704 + 413511680
+
+
 def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms_per_pass: float) -> dict:
     """Per-kernel figures of one pass from the eager event pairs: the dense GEMM at 4096 rows
     (tensor roof), the one-pass decode (HBM roof) and the time share of each entry point."""
@@ -646,10 +652,16 @@ def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms
             "peak_source": f"{peak_src} sustained cuBLAS bf16 (the kernel runs inside a seconds-long loop)",
             "launch_ms_sum": round(ms, 4), "launch_ms_gate": None if not big else round(big, 4),
             "TFLOPs_per_linear": per_linear, "share_of_pass": round(ms / total, 3),
-            # dram__bytes_read + write of the gate-shaped launch, ncu capture of a 4096 x 7168 x 8192
-            # case scaled by N (traffic grows with N at fixed M, K): profiles/gemm_c5_gate_rows4096.md
-            "traffic": None,
         }
+        # dram__bytes_read.sum + dram__bytes_write.sum of the gate launch (4096 x 28672 x 8192), one ncu
+        # capture (profiles/gemm_tcgen05_c5_gate_rows4096.md); a shard's launch is scaled by its columns
+        gate_n = local_n("gate", 28672)
+        out["gemm_roofline"].update({
+            "traffic": int(NCU_GATE_GEMM_DRAM_BYTES * gate_n / 28672),
+            "traffic_of": "the gate launch (launch_ms_gate), ncu capture of the unsharded launch"
+                          + ("" if gate_n == 28672 else " scaled by this rank's columns"),
+            "algorithmic_bytes_gate": 2 * (4096 * 8192 + gate_n * 8192 + 4096 * gate_n),
+        })
     dec = [(name, n, k, rows, kmean.get(("npb_vq_decode", (name, rows)))) for name, n, k in C5_LINEARS
            for rows in C5_ROWS]
     dec = [d for d in dec if d[4]]
@@ -662,7 +674,12 @@ def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms
             "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": f"{peak_src} copy bandwidth",
             "algorithmic_bytes": nbytes, "launch_ms_sum": round(dms, 4), "launches_per_pass": len(dec),
-            "share_of_pass": round(dms / total, 3), "traffic": None,
+            "share_of_pass": round(dms / total, 3),
+            # measured on the gate decode (59.8 MB read + 413.5 MB written of 58.7 + 1.0 + 469.8 MB
+            # algorithmic: the tail of the output is still dirty in L2 when the kernel ends), applied
+            # to the pass by the same ratio
+            "traffic": int(nbytes * NCU_GATE_DECODE_DRAM_BYTES / (28672 * 1024 * 2 + 28672 * 8192 * 2)),
+            "traffic_of": "all decode launches of a pass, from the ncu capture of the gate decode",
         }
     gem = out.get("gemm_roofline")
     dcr = out.get("decode_roofline")
@@ -826,7 +843,7 @@ def run_c3(device, peaks, peak_src) -> dict:
             tag = f"{'hqq_g64' if asym else 'q4_0_g32'}_{n_out}x{K_IN}"
             out[tag] = {"packed_bytes": nbytes, "bands": table}
             if n_out == 14336 and not asym:
-                out["q4_gemv_roofline"] = _gemv_roofline("npb_q_gemv at 1 row (q4_gemv_mma_rows8_kernel), Q4_0 g32 "
+                out["q4_gemv_roofline"] = _gemv_roofline("npb_q_gemv at 1 row (q4_gemv_ring_kernel), Q4_0 g32 "
                                                          "14336x4096", table["1"]["ms"], nbytes, peaks, peak_src)
                 g = table["4096"]["kernels_eager_ms"].get("npb_gemm")
                 if g:
@@ -1097,6 +1114,7 @@ def run_case(args) -> dict:
       vqs16:ROWS / vqs12:ROWS   the same shape with 4096-entry codebooks per 2048 columns
       q40:ROWS / hqq:ROWS       group-affine 14336 x 4096
       c5:NAME:ROWS one linear of the headline layer set (NAME in q k v o gate up down)
+      c5pass       the headline layer set, eager passes (the launch list)
       probes       the hardware-rate probes; c4 the decoder stack"""
     from neuropress_b200 import kernels
 
@@ -1105,6 +1123,21 @@ def run_case(args) -> dict:
     peaks, peak_src = load_peaks()
     parts = args.case.split(":")
     name = parts[0]
+    if name == "c5pass":   # the headline workload, eager: one warm-up pass, then --steps passes (launch list)
+        wl = C5(device, 0, 1, False)
+        timer = KernelTimer()
+        wl.run_pass(0)
+        torch.cuda.synchronize()
+        kernels.set_launch_hook(timer)
+        for q in range(args.steps):
+            wl.run_pass(q + 1, timer=timer)
+        torch.cuda.synchronize()
+        kernels.set_launch_hook(None)
+        per: dict[str, list] = {}
+        for (sym, tag), v in timer.mean_ms().items():
+            per.setdefault(sym, []).append(v)
+        return {"case": "c5pass", "passes": args.steps, "launches_per_pass": timer.count // max(args.steps, 1),
+                "ms_per_pass_by_entry_point": {k: round(sum(v), 4) for k, v in per.items()}}
     if name == "probes":
         return run_probes(device, peaks)
     if name == "c4":

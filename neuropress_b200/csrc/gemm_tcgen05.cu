@@ -59,6 +59,7 @@ struct GemmParams {
   void* y;
   int M, N, K;
   int tiles_m, tiles_n;
+  int group_m;  // tiles are walked in bands of group_m tile rows (see tile_coords)
   FusedQ4 q4;
   GatherSink sink;  // peer_out != null: y goes to every rank's buffer, then the handshake
   uint64_t wait_ns;  // limit of every mbarrier wait (npb_set_wait_limit_ns; 2 s by default)
@@ -80,6 +81,19 @@ constexpr int kQ4DecodeWarps = 24;
 template <int BN, int MT>
 constexpr int q4_stages() {
   return SmemLayout<BN, MT>::stages(kSmemCapAssumed) > 6 ? 6 : SmemLayout<BN, MT>::stages(kSmemCapAssumed);
+}
+
+// Tile order.  Tiles are walked in bands of group_m tile rows: inside a band the tile row runs
+// fastest, then the tile column, so a wave of CTAs works on (a few tile columns) x (group_m tile
+// rows) and the band's activation rows stay L2-resident while all of W streams past them once.
+// group_m == tiles_m is the plain column-by-column walk.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& tm, int& tn) {
+  const int per_band = p.group_m * p.tiles_n;
+  const int band = t / per_band, r = t - band * per_band;
+  const int m0 = band * p.group_m;
+  const int gm = min(p.group_m, p.tiles_m - m0);
+  tn = r / gm;
+  tm = m0 + (r - tn * gm);
 }
 
 // ---- B tile decoders (fused modes) ---------------------------------------------------------
@@ -228,7 +242,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        int tm, tn;
+        tile_coords(p, t, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1, abort_flag, p.wait_ns,
                                  BMODE == B_TMA ? 0u : 128u)) {
@@ -306,7 +321,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      int tm, tn;
+      tile_coords(p, t, tm, tn);
       const int buf = (NBUF == 2) ? (it & 1) : 0;
       const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
       // All lanes wait (each needs the acquire), then agree on the outcome so that the
@@ -438,7 +454,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool asym = p.q4.has_zp != 0;
         const uint32_t b_stage = smem_u32(stage_base + (size_t)slot * kStageBytes + MT * kAStageBytes);
         auto warp_n0 = [&](int i) {
-          return ((blockIdx.x + (i / num_kb) * gridDim.x) / p.tiles_m) * BN + row0;
+          int tm, tn;
+          tile_coords(p, blockIdx.x + (i / num_kb) * gridDim.x, tm, tn);
+          return tn * BN + row0;
         };
         // Decode item i from `cur` while this warp's next item, i + S, is fetched into `nxt`.
         auto step = [&](Q4Item<RPL>& cur, Q4Item<RPL>& nxt, int i) -> bool {
@@ -521,6 +539,24 @@ int make_tmap(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, in
   return NPB_OK;
 }
 
+// Band height of the tile walk, from a traffic estimate: a band whose activation rows fit the L2
+// share that survives next to the streaming W and y traffic is read from HBM once, a larger one
+// once per wave of CTAs; W is read once per band.
+int pick_group_m(int tiles_m, int tiles_n, int tile_rows, int bn, int K, int ctas) {
+  const double kResident = 40e6;
+  const double x_tile = (double)tile_rows * K * 2, w_all = (double)tiles_n * bn * K * 2;
+  double best = 1e300;
+  int best_g = tiles_m;
+  for (int g = tiles_m; g >= 1; g = g > 1 ? (g + 1) / 2 : 0) {
+    const int bands = (tiles_m + g - 1) / g;
+    const double waves = (double)g * tiles_n / ctas;
+    const double x_reads = g * x_tile <= kResident ? 1.0 : (waves > 1.0 ? waves : 1.0);
+    const double traffic = x_reads * g * x_tile * bands + w_all * bands;
+    if (traffic < best * 0.98) { best = traffic; best_g = g; }
+  }
+  return best_g;
+}
+
 template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER = false>
 int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t st) {
   constexpr bool bf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -553,6 +589,7 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
+  p.group_m = BMODE == B_TMA ? pick_group_m(p.tiles_m, p.tiles_n, BM * MT, BN, p.K, grid) : p.tiles_m;
   constexpr int threads = BMODE == B_TMA ? 192 : 192 + 32 * kQ4DecodeWarps;
   kern<<<grid, threads, smem, st>>>(ta, tb, p, stages);
   NPB_LAUNCH_CHECK();
