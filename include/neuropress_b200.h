@@ -272,6 +272,16 @@ int npb_gemm_device_status(int* host_out);
 int npb_set_wait_limit_ns(uint64_t ns);
 uint64_t npb_get_wait_limit_ns(void);
 
+/* Tile policy of the dense GEMM (npb_gemm, npb_gemm_allgather, the large-batch band of the
+ * linears): 0 = every tile by one CTA (tcgen05 cta_group::1); 1 = automatic (default): CTA
+ * pairs (cta_group::2, 256-row tiles, each CTA stages half of the W tile) where the row count
+ * fills pair tiles and there is a tile for every pair; 2 = pairs for every launch of more than
+ * 128 rows.  Every mode accumulates the same products in fp32 in the same order along K.
+ * Process-wide, read at launch; the environment variable NEUROPRESS_B200_GEMM_PAIRS
+ * gives the initial value.  No reference counterpart (the reference calls cuBLAS). */
+int npb_set_gemm_pair_mode(int mode);
+int npb_get_gemm_pair_mode(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -47,6 +47,8 @@ EXPORTED_SYMBOLS = (
     "npb_gemm_device_status",
     "npb_set_wait_limit_ns",
     "npb_get_wait_limit_ns",
+    "npb_set_gemm_pair_mode",
+    "npb_get_gemm_pair_mode",
 )
 
 
@@ -151,6 +153,8 @@ def load_library() -> ctypes.CDLL:
     lib.npb_gemm_device_status.argtypes = [POINTER(c_int)]
     lib.npb_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     lib.npb_get_wait_limit_ns.argtypes = []
+    lib.npb_set_gemm_pair_mode.argtypes = [c_int]
+    lib.npb_get_gemm_pair_mode.argtypes = []
     for name in EXPORTED_SYMBOLS[3:]:
         getattr(lib, name).restype = c_int
     lib.npb_get_wait_limit_ns.restype = ctypes.c_uint64

@@ -1,6 +1,7 @@
 // extern "C" surface of libneuropress_b200.so: argument validation, status strings and the
 // thin forwarding layer onto the kernels.  No torch types, no allocation, no host sync.
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -50,6 +51,14 @@ static thread_local char g_last_error[256] = "";
 
 static std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
 uint64_t wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
+
+// 0 never, 1 where the shape fills pair tiles (default), 2 for every dense GEMM of more than
+// 128 rows.  NEUROPRESS_B200_GEMM_PAIRS gives the initial value.
+static std::atomic<int> g_gemm_pair_mode{[] {
+  const char* e = getenv("NEUROPRESS_B200_GEMM_PAIRS");
+  return (e && e[0] >= '0' && e[0] <= '2' && e[1] == 0) ? e[0] - '0' : 1;
+}()};
+int gemm_pair_mode() { return g_gemm_pair_mode.load(std::memory_order_relaxed); }
 
 void set_last_cuda_error(cudaError_t e, const char* where) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorName(e),
@@ -288,5 +297,13 @@ int npb_set_wait_limit_ns(uint64_t ns) {
 }
 
 uint64_t npb_get_wait_limit_ns(void) { return npb::wait_limit_ns(); }
+
+int npb_set_gemm_pair_mode(int mode) {
+  if (mode < 0 || mode > 2) return NPB_ERR_INVALID_ARG;
+  npb::g_gemm_pair_mode.store(mode, std::memory_order_relaxed);
+  return NPB_OK;
+}
+
+int npb_get_gemm_pair_mode(void) { return npb::gemm_pair_mode(); }
 
 }  // extern "C"

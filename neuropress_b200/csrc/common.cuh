@@ -38,6 +38,8 @@ inline bool aligned_to(const void* p, size_t a) {
 // Limit, in nanoseconds, of every bounded in-kernel wait (mbarriers of the GEMMs, peer flags of
 // the all-gather): 2 s unless npb_set_wait_limit_ns changed it.  Read at launch time.
 uint64_t wait_limit_ns();
+// Tile shape policy of the dense GEMM (npb_set_gemm_pair_mode): 0 single CTAs, 1 automatic, 2 pairs.
+int gemm_pair_mode();
 
 // Number of SMs of the current device (cached per device id).
 int sm_count();

@@ -175,7 +175,11 @@ __device__ __forceinline__ void q4_emit(const Q4Item<RPL>& it, int n0, int N, ui
 // ---- the kernel ------------------------------------------------------------------------------
 // GATHER: the epilogue carries the fused all-gather (dense mode only); a separate instantiation
 // so that the plain kernels do not pay for its registers.
-template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER>
+// CG = 2 (dense mode, MT = 1): two CTAs of a cluster share one 256 x BN tile -- each loads its own
+// 128 rows of x and its own BN/2 rows of W, the even CTA issues tcgen05.mma.cta_group::2 for both,
+// each CTA's TMEM gets the accumulator rows of its own x rows.  Half the W bytes per stage and CTA
+// means a deeper ring (7 stages instead of 4 at BN = 256) for the same shared memory.
+template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER, int CG = 1>
 __global__ void __launch_bounds__(BMODE == B_TMA ? 192 : 192 + 32 * kQ4DecodeWarps, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const GemmParams p, const int stages) {
@@ -184,14 +188,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   constexpr int TMEM_COLS = (NBUF * ACC_COLS <= 32) ? 32 : (NBUF * ACC_COLS <= 64) ? 64
                           : (NBUF * ACC_COLS <= 128) ? 128 : (NBUF * ACC_COLS <= 256) ? 256 : 512;
   constexpr int BUF_STRIDE = (NBUF == 2) ? TMEM_COLS / 2 : 0;
-  constexpr int kStageBytes = SmemLayout<BN, MT>::kStageBytes;
+  constexpr int kStageBytes = SmemLayout<BN / CG, MT>::kStageBytes;
   // Q4: S stages x R warps per stage (see the decoder notes); VQ: four warps share every stage.
   constexpr int kQ4Stages = q4_stages<BN, MT>();
   constexpr int kQ4WarpsPerStage = 4;
   constexpr int kNumDecodeWarps = (BMODE == B_TMA) ? 0 : kQ4Stages * kQ4WarpsPerStage;
   constexpr int kFullArrivals = (BMODE == B_TMA) ? 0 : kQ4WarpsPerStage;
   static_assert(BMODE != B_Q4 || kNumDecodeWarps <= kQ4DecodeWarps, "decode warps of the Q4 launch");
-  constexpr uint32_t kIdesc = umma_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
+  constexpr uint32_t kIdesc = umma_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM * CG, BN);
+  static_assert(CG == 1 || (CG == 2 && BMODE == B_TMA && MT == 1 && BN % 32 == 0), "CTA pairs: dense mode only");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
   static_assert(BMODE == B_TMA || BN == 128, "fused decode maps one decode thread to one W row");
 
@@ -205,12 +210,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* epi_got = abort_flag + 1;  // [2][4]: outcome of each epilogue warp's wait, per tile parity
-  uint8_t* stage_base = smem + SmemLayout<BN, MT>::kBarrierBytes;
+  uint8_t* stage_base = smem + SmemLayout<BN / CG, MT>::kBarrierBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (p.K + BK - 1) / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  // Tile walk of this CTA (pair): tiles first_tile, first_tile + tile_stride, ...
+  const int cta_rank = CG == 2 ? (int)cluster_ctarank() : 0;
+  const int first_tile = blockIdx.x / CG, tile_stride = gridDim.x / CG;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -220,18 +228,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 4);  // one arrive per epilogue warp
+      mbar_init(&tmem_empty[b], 4 * CG);  // one arrive per epilogue warp (of both CTAs of a pair)
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     if (BMODE == B_TMA) tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (CG == 2) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (CG == 2) {
+    __syncwarp();
+    cluster_sync_all();  // the peer's barriers are initialised before anything is sent to them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -241,7 +259,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      // pair mode: all bytes of a stage, both CTAs', are credited to the leader's full barrier
+      const uint32_t full0 = CG == 2 ? map_to_cta(smem_u32(&full_bar[0]), 0) : 0u;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride) {
         int tm, tn;
         tile_coords(p, t, tm, tn);
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -253,25 +273,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           uint8_t* st = stage_base + (size_t)s * kStageBytes;
           constexpr uint32_t tx = MT * kAStageBytes + (BMODE == B_TMA ? BN * BK * 2 : 0);
-          mbar_arrive_expect_tx(&full_bar[s], tx);
+          if (CG == 2) {
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], tx + kAStageBytes);  // 2 A tiles + all of B
+            const uint32_t bar = full0 + (uint32_t)s * 8u;
+            tma_load_2d_pair(st, &tmap_a, bar, kb * BK, (tm * 2 + cta_rank) * BM);
+            tma_load_2d_pair(st + kAStageBytes, &tmap_b, bar, kb * BK, tn * BN + cta_rank * (BN / 2));
+          } else {
+            mbar_arrive_expect_tx(&full_bar[s], tx);
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            tma_load_2d(st + mt * kAStageBytes, &tmap_a, &full_bar[s], kb * BK,
-                        (tm * MT + mt) * BM);
-          if (BMODE == B_TMA)
-            tma_load_2d(st + MT * kAStageBytes, &tmap_b, &full_bar[s], kb * BK, tn * BN);
+            for (int mt = 0; mt < MT; ++mt)
+              tma_load_2d(st + mt * kAStageBytes, &tmap_a, &full_bar[s], kb * BK,
+                          (tm * MT + mt) * BM);
+            if (BMODE == B_TMA)
+              tma_load_2d(st + MT * kAStageBytes, &tmap_b, &full_bar[s], kb * BK, tn * BN);
+          }
           if (++s == stages) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
         const int buf = (NBUF == 2) ? (it & 1) : 0;
         const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
         if (!mbar_wait_bounded(&tmem_empty[buf], buf_ph ^ 1, abort_flag, p.wait_ns)) {
@@ -295,14 +322,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               // +32 bytes per K step inside the 128-byte swizzle row: +2 in the >>4 field
-              umma_f16(acc + mt * BN, adesc + 2 * k, bdesc + 2 * k, kIdesc,
-                       (kb > 0 || k > 0) ? 1u : 0u);
+              if (CG == 2)
+                umma_f16_pair(acc, adesc + 2 * k, bdesc + 2 * k, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+              else
+                umma_f16(acc + mt * BN, adesc + 2 * k, bdesc + 2 * k, kIdesc,
+                         (kb > 0 || k > 0) ? 1u : 0u);
             }
           }
-          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if (CG == 2) umma_commit_pair(&empty_bar[s]);
+          else umma_commit(&empty_bar[s]);
           if (++s == stages) { s = 0; ph ^= 1; }
         }
-        if (ok) umma_commit(&tmem_full[buf]);
+        if (ok) {
+          if (CG == 2) umma_commit_pair(&tmem_full[buf]);
+          else umma_commit(&tmem_full[buf]);
+        }
       }
     }
   } else if (warp < 6) {
@@ -320,9 +355,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (gathered) y = static_cast<T*>(p.sink.peer_out[p.sink.rank]);
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    const uint32_t empty0 = CG == 2 ? map_to_cta(smem_u32(&tmem_empty[0]), 0) : 0u;  // the leader's
+    for (int t = first_tile; t < num_tiles && ok; t += tile_stride, ++it) {
       int tm, tn;
       tile_coords(p, t, tm, tn);
+      if (CG == 2) tm = tm * 2 + cta_rank;  // this CTA's 128 rows of the pair's 256
       const int buf = (NBUF == 2) ? (it & 1) : 0;
       const uint32_t buf_ph = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
       // All lanes wait (each needs the acquire), then agree on the outcome so that the
@@ -398,7 +435,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      if (lane == 0) {
+        if (CG == 2) mbar_arrive_remote(empty0 + (uint32_t)buf * 8u);
+        else mbar_arrive(&tmem_empty[buf]);
+      }
       if (gathered && p.sink.world > 1) {
         // copy the finished tile to the peers (N, ld and col0 are multiples of 8 elements)
         asm volatile("bar.sync 1, 128;" ::: "memory");  // all four warps' rows are stored
@@ -491,10 +531,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   tc_fence_before();
-  __syncthreads();
+  if (CG == 2) {
+    // Nothing of the peer may be touched after it left: its TMEM by the leader's MMAs, the
+    // leader's barriers by the peer's copies and arrives.
+    __syncwarp();
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -557,19 +605,20 @@ int pick_group_m(int tiles_m, int tiles_n, int tile_rows, int bn, int K, int cta
   return best_g;
 }
 
-template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER = false>
+template <typename T, int BN, int MT, int BMODE, int BITS, bool GATHER = false, int CG = 1>
 int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t st) {
   constexpr bool bf16 = std::is_same<T, __nv_bfloat16>::value;
-  auto kern = gemm_kernel<T, BN, MT, BMODE, BITS, GATHER>;
+  auto kern = gemm_kernel<T, BN, MT, BMODE, BITS, GATHER, CG>;
+  using Layout = SmemLayout<BN / CG, MT>;  // a CTA of a pair holds half of the W tile
   const int cap = max_dynamic_smem();
-  int stages = SmemLayout<BN, MT>::stages(cap);
+  int stages = Layout::stages(cap);
   if (stages < 2) return NPB_ERR_UNSUPPORTED;
   // The 4-bit decoder binds its warps to ring stages at compile time.
   if (BMODE == B_Q4) {
     if (stages < q4_stages<BN, MT>()) return NPB_ERR_UNSUPPORTED;
     stages = q4_stages<BN, MT>();
   }
-  const int smem = SmemLayout<BN, MT>::kBarrierBytes + 1024 + stages * SmemLayout<BN, MT>::kStageBytes;
+  const int smem = Layout::kBarrierBytes + 1024 + stages * Layout::kStageBytes;
   static int configured[64] = {0};
   int dev = 0;
   NPB_CUDA_TRY(cudaGetDevice(&dev));
@@ -580,28 +629,58 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
   CUtensorMap ta, tb;
   if (int rc = make_tmap(&ta, x, p.M, p.K, BM, bf16)) return rc;
   if (BMODE == B_TMA) {
-    if (int rc = make_tmap(&tb, w_dense, p.N, p.K, BN, bf16)) return rc;
+    if (int rc = make_tmap(&tb, w_dense, p.N, p.K, BN / CG, bf16)) return rc;
   } else {
     tb = ta;
   }
   p.wait_ns = wait_limit_ns();
-  p.tiles_m = (p.M + BM * MT - 1) / (BM * MT);
+  p.tiles_m = (p.M + BM * MT * CG - 1) / (BM * MT * CG);
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  p.group_m = BMODE == B_TMA ? pick_group_m(p.tiles_m, p.tiles_n, BM * MT, BN, p.K, grid) : p.tiles_m;
   constexpr int threads = BMODE == B_TMA ? 192 : 192 + 32 * kQ4DecodeWarps;
-  kern<<<grid, threads, smem, st>>>(ta, tb, p, stages);
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr{};
+  int slots = sm_count() / CG;  // CTAs, or CTA pairs, that run at once
+  if (CG == 2) {
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = CG;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    // pairs that can be resident together (both CTAs of a pair sit in one GPC)
+    static int resident_pairs[64] = {0};
+    if (dev >= 0 && dev < 64) {
+      if (resident_pairs[dev] == 0) {
+        cfg.gridDim = dim3(slots * CG);
+        int n = 0;
+        NPB_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+        resident_pairs[dev] = n > 0 ? n : 1;
+      }
+      if (resident_pairs[dev] < slots) slots = resident_pairs[dev];
+    }
+  }
+  const int units = tiles < slots ? tiles : slots;
+  p.group_m = BMODE == B_TMA ? pick_group_m(p.tiles_m, p.tiles_n, BM * MT * CG, BN, p.K, units) : p.tiles_m;
+  if (CG == 1) {
+    kern<<<units, threads, smem, st>>>(ta, tb, p, stages);
+  } else {
+    cfg.gridDim = dim3(units * CG);
+    NPB_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, ta, tb, p, stages));
+  }
   NPB_LAUNCH_CHECK();
   return NPB_OK;
 }
 
 // Tile width for the dense GEMM: minimise (waves x tile cost) with a mild preference for
 // wide tiles (fewer shared-memory bytes per flop).
-int pick_bn(int64_t M, int64_t N) {
+int pick_bn(int64_t M, int64_t N, int cg) {
   const int cands[5] = {256, 224, 192, 128, 64};
-  const int sms = sm_count();
-  const int64_t tm = (M + BM - 1) / BM;
+  const int sms = sm_count() / cg;
+  const int64_t tm = (M + BM * cg - 1) / (BM * cg);
   double best = 1e30;
   int best_bn = 256;
   for (int bn : cands) {
@@ -614,9 +693,29 @@ int pick_bn(int64_t M, int64_t N) {
   return best_bn;
 }
 
+// CTA pairs pay when the rows fill 256-row tiles (at most 1/8 of the pair rows empty) and there
+// are enough tiles to keep every pair busy.
+bool use_pairs(int64_t M, int64_t N) {
+  const int mode = gemm_pair_mode();
+  if (mode == 0 || M <= BM) return false;
+  if (mode == 2) return true;
+  const int64_t rows1 = (M + BM - 1) / BM * BM, rows2 = (M + 2 * BM - 1) / (2 * BM) * (2 * BM);
+  if (rows2 * 8 > rows1 * 9) return false;
+  return (rows2 / (2 * BM)) * ((N + 255) / 256) >= sm_count() / 2;
+}
+
 template <typename T, bool GATHER>
 int gemm_dense(const void* x, const void* w, GemmParams p, cudaStream_t st) {
-  switch (pick_bn(p.M, p.N)) {
+  if (use_pairs(p.M, p.N)) {
+    switch (pick_bn(p.M, p.N, 2)) {
+      case 256: return launch_gemm<T, 256, 1, B_TMA, 0, GATHER, 2>(x, w, p, st);
+      case 224: return launch_gemm<T, 224, 1, B_TMA, 0, GATHER, 2>(x, w, p, st);
+      case 192: return launch_gemm<T, 192, 1, B_TMA, 0, GATHER, 2>(x, w, p, st);
+      case 128: return launch_gemm<T, 128, 1, B_TMA, 0, GATHER, 2>(x, w, p, st);
+      default: return launch_gemm<T, 64, 1, B_TMA, 0, GATHER, 2>(x, w, p, st);
+    }
+  }
+  switch (pick_bn(p.M, p.N, 1)) {
     case 256: return launch_gemm<T, 256, 1, B_TMA, 0, GATHER>(x, w, p, st);
     case 224: return launch_gemm<T, 224, 1, B_TMA, 0, GATHER>(x, w, p, st);
     case 192: return launch_gemm<T, 192, 1, B_TMA, 0, GATHER>(x, w, p, st);

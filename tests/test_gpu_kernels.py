@@ -208,6 +208,47 @@ def test_dense_gemm_matches_fp32_reference(shape, dtype):
     assert_output_close(y, ref, dtype, tol=2e-3)
 
 
+PAIR_SHAPES = [(256, 512, 1024), (130, 72, 96), (384, 1000, 192), (640, 4096, 512), (1000, 2056, 320),
+               (2048, 1024, 512), (300, 14336, 256), (4096, 4736, 1024), (129, 16, 64)]
+
+
+@pytest.mark.parametrize("shape", PAIR_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dense_gemm_cta_pairs(shape, dtype):
+    """The cta_group::2 form of the dense GEMM (two CTAs per 256-row tile), forced on for shapes
+    the automatic policy would leave to single CTAs too: row counts that leave the second CTA of
+    the last pair without rows (130, 384, 640), N and K tails, many tiles per pair (banded walk).
+    Against fp64, and bit-for-bit against the single-CTA form (same products, same K order)."""
+    from neuropress_b200 import _cabi
+    lib = _cabi.load_library()
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(dtype).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    before = lib.npb_get_gemm_pair_mode()
+    try:
+        assert lib.npb_set_gemm_pair_mode(2) == 0
+        y_pair = kernels.gemm(x, w, b)
+        assert _cabi.gemm_device_status() == 0
+        assert lib.npb_set_gemm_pair_mode(0) == 0
+        y_single = kernels.gemm(x, w, b)
+        assert _cabi.gemm_device_status() == 0
+    finally:
+        lib.npb_set_gemm_pair_mode(before)
+    ref = x.double().cpu() @ w.double().cpu().T + b.double().cpu()
+    assert_output_close(y_pair, ref, dtype, tol=2e-3)
+    assert torch.equal(y_pair, y_single)
+
+
+def test_gemm_pair_mode_setter_validates():
+    from neuropress_b200 import _cabi
+    lib = _cabi.load_library()
+    before = lib.npb_get_gemm_pair_mode()
+    assert lib.npb_set_gemm_pair_mode(3) == 1 and lib.npb_set_gemm_pair_mode(-1) == 1
+    assert lib.npb_get_gemm_pair_mode() == before
+
+
 # ----------------------------------------------------------------- tile-decode GEMMs ---
 FUSED_CASES = [
     (256, 512, 4096, 16, 0, False, 0),
