@@ -66,7 +66,7 @@ C5_INPUT = {"q": "h", "k": "h", "v": "h", "gate": "h", "up": "h", "o": "a", "dow
 C5_INPUT_WIDTH = {"h": 8192, "a": 8192, "m": 28672}
 PASSES_PER_STEP = 8
 N_COPIES = 2
-SHARD_MIN_BYTES = 32 << 20       # index-stream bytes from which a linear is sharded at N > 1
+SHARD_MIN_BYTES = 8 << 20        # index-stream bytes from which a linear is sharded at N > 1
 TOKENS_PER_PASS = sum(C5_ROWS)
 PARITY_TOL = 1e-2
 

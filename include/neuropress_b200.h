@@ -148,6 +148,24 @@ int npb_gemm(const void* x, const void* w, const float* bias, void* y, int64_t M
 int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
                       int64_t N, int64_t K, const float* bias, void* y, npb_stream_t stream);
 
+/* The copy form of the tile-decode GEMM for plain weights (no residual codebook, no row scale).
+ * A decoded vector of such a weight is its codebook entry cast to the activation type, so with
+ * the codebook already in that type the decode is a 16-byte copy, which the kernel issues as
+ * asynchronous global -> shared copies (no register destination, nothing waits for a gather).
+ *   npb_vq_codebook_cast: out[i] = dtype(centroids[i]) for n_values = entries * vector_len fp16
+ *     values (NPB_F16 copies).  Done once per codebook and activation type by the caller.
+ *   npb_vq_gemm_fused_cb: npb_vq_gemm_fused with codebook_x = that table ([n_codebooks *
+ *     num_centroids, 8] of x_dtype, 16-byte aligned; for NPB_F16 w->centroids itself will do).
+ *     Same results bit for bit.  NPB_ERR_UNSUPPORTED for weights with a residual or a row scale
+ *     and for index streams that do not allow wide reads (bits other than 8 / 12 / 16,
+ *     unaligned stream): call npb_vq_gemm_fused for those.
+ * Replaces the same reference code as npb_vq_gemm_fused. */
+int npb_vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int out_dtype,
+                         npb_stream_t stream);
+int npb_vq_gemm_fused_cb(const npb_vq_weight* w, const void* codebook_x, const void* x, int x_dtype,
+                         int64_t M, int64_t N, int64_t K, const float* bias, void* y,
+                         npb_stream_t stream);
+
 /* Same for group-affine weights (no reference counterpart beyond q_linear, which re-reads
  * the weight per row: neuropress/kernels/q4_linear.cu:80-131). nbits 4, K % 64 == 0,
  * group_size % 32 == 0 (NPB_ERR_UNSUPPORTED otherwise: decode, then npb_gemm). */

@@ -36,6 +36,8 @@ EXPORTED_SYMBOLS = (
     "npb_vq_gemv_grouped",
     "npb_gemm",
     "npb_vq_gemm_fused",
+    "npb_vq_gemm_fused_cb",
+    "npb_vq_codebook_cast",
     "npb_q_gemm_fused",
     "npb_vq_linear_static_scratch",
     "npb_allgather_push",
@@ -133,6 +135,8 @@ def load_library() -> ctypes.CDLL:
     lib.npb_vq_gemv_grouped.argtypes = [vq_p, c_int, POINTER(c_int64), POINTER(c_void_p), c_void_p, c_int, c_int64,
                                         c_int64, c_void_p, ctypes.c_float, c_void_p, c_void_p]
     lib.npb_vq_gemm_fused.argtypes = [vq_p, *gemv_tail]
+    lib.npb_vq_gemm_fused_cb.argtypes = [vq_p, c_void_p, *gemv_tail]
+    lib.npb_vq_codebook_cast.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_void_p]
     lib.npb_vq_linear_static_scratch.argtypes = [vq_p, *gemv_tail]
     lib.npb_q_gemm_fused.argtypes = [q_p, *gemv_tail]
     lib.npb_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -23,7 +23,8 @@ int q_gemv(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, con
            cudaStream_t);
 int gemm(const void*, const void*, const float*, void*, int64_t, int64_t, int64_t, int,
          cudaStream_t);
-int vq_gemm_fused(const npb_vq_weight*, const void*, int, int64_t, int64_t, int64_t,
+int vq_codebook_cast(const void*, int64_t, void*, int, cudaStream_t);
+int vq_gemm_fused(const npb_vq_weight*, const void*, const void*, int, int64_t, int64_t, int64_t,
                   const float*, void*, cudaStream_t);
 int q_gemm_fused(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, const float*,
                  void*, cudaStream_t);
@@ -220,7 +221,17 @@ int npb_gemm(const void* x, const void* w, const float* bias, void* y, int64_t M
 
 int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
                       int64_t N, int64_t K, const float* bias, void* y, npb_stream_t stream) {
-  return npb::vq_gemm_fused(w, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+  return npb::vq_gemm_fused(w, nullptr, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int out_dtype, npb_stream_t stream) {
+  return npb::vq_codebook_cast(centroids, n_values, out, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_gemm_fused_cb(const npb_vq_weight* w, const void* codebook_x, const void* x, int x_dtype, int64_t M,
+                         int64_t N, int64_t K, const float* bias, void* y, npb_stream_t stream) {
+  if (codebook_x == nullptr) return NPB_ERR_INVALID_ARG;
+  return npb::vq_gemm_fused(w, codebook_x, x, x_dtype, M, N, K, bias, y, static_cast<cudaStream_t>(stream));
 }
 
 int npb_q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N,

@@ -21,6 +21,15 @@
 //     single st.shared.v4 at chunk (c ^ (row & 7)) of its 128-byte row.
 //   * Residual codebook (<= 256 entries) staged in shared memory; row scale in a register.
 //
+// Copy form (plain weights: no residual, no row scale).  A decoded vector of such a weight is the
+// codebook entry itself, cast to the activation type -- a pure function of the entry.  Given the
+// codebook already in the activation type (npb_vq_codebook_cast; the fp16 codebook itself for
+// fp16 activations), decoding a vector is a 16-byte copy from the table to its swizzle chunk,
+// and the decode warps issue it as cp.async (global -> shared, no register destination) with
+// cp.async.mbarrier.arrive on the stage's full barrier: nothing in the decode warps ever waits
+// for a gather, and the number of gathers in flight is bounded by the ring (stages x BN x 8),
+// not by registers.
+//
 // Weights are rounded exactly as the one-pass decode rounds them (fp16 add / multiply, one
 // rounding to the activation type), so this band and decode + dense GEMM differ only in the
 // order of the fp32 accumulation.  Every mbarrier wait is bounded (see tcgen05.cuh).
@@ -55,6 +64,7 @@ struct FusedParams {
   const uint8_t* packed;
   int64_t packed_bytes;
   const __half* centroids;
+  const void* cb_x;              // copy form: the codebook in the activation type, else null
   const uint8_t* res_packed;     // never null: aliases `packed` when there is no residual
   int64_t res_bytes;
   const __half* res_centroids;   // never null: aliases `centroids`
@@ -64,6 +74,7 @@ struct FusedParams {
   uint64_t wait_ns;
   int bits, res_bits, num_centroids, groups_per_codebook, cb_rows, res_rows;
   int has_res, has_scale;
+  int clamp;                     // copy form: indices can exceed the codebook (NC < 2^bits) or take an offset
   int M, N, K, BN, tiles_m, tiles_n, groups, warps_per_group;
 };
 
@@ -196,7 +207,39 @@ __device__ __forceinline__ void emit_row(const RawRow<BITS>& it, const FusedPara
   }
 }
 
-template <typename T, int MT, int BITS>
+// 16-byte asynchronous copy global -> shared through L2 only; src_bytes = 0 writes zeros.
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// The barrier gets one arrival from this thread once all its cp.async issued so far have landed
+// (counted in the barrier's expected arrivals: .noinc).
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Copy form of emit_row: the eight vectors of (row n, k block kb) go from the activation-type
+// codebook to their swizzle chunks as asynchronous copies.
+template <int BITS>
+__device__ __forceinline__ void emit_row_copy(const RawRow<BITS>& it, const FusedParams& p, bool valid, int kb,
+                                              uint32_t b_stage, int row) {
+  // chunk c of tile row `row` lives at (row * 128) + ((c ^ (row & 7)) << 4) = base ^ (c << 4)
+  const uint32_t base = b_stage + row * 128 + ((row & 7) << 4);
+  uint32_t idx[8];
+  expand_row<BITS>(it, idx);
+  if (p.clamp) {
+    const uint32_t off = p.groups_per_codebook > 0
+                             ? (uint32_t)((kb * 8) / p.groups_per_codebook) * (uint32_t)p.num_centroids : 0u;
+    const uint32_t last = (uint32_t)p.cb_rows - 1u;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) idx[c] = min(idx[c] + off, last);
+  }
+  const char* cb = static_cast<const char*>(p.cb_x);
+  const uint32_t nbytes = valid ? 16u : 0u;  // rows past N: zeros (their columns are never stored)
+#pragma unroll
+  for (int c = 0; c < 8; ++c) cp_async_16(base ^ (uint32_t)(c << 4), cb + ((size_t)idx[c] << 4), nbytes);
+}
+
+template <typename T, int MT, int BITS, bool COPY>
 __global__ void __launch_bounds__(kThreads, 1)
 vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -225,7 +268,8 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < G; ++s) {
-      mbar_init(&full_bar[s], 1 + p.warps_per_group);  // TMA producer's expect_tx arrive + one per decode warp
+      // TMA producer's expect_tx arrive + one per decode warp (copy form: one per decode lane)
+      mbar_init(&full_bar[s], 1 + (COPY ? 32 : 1) * p.warps_per_group);
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -293,6 +337,7 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
             break;
           }
           tc_fence_after();
+          if (COPY) fence_proxy_async_smem();  // the W tile was written by cp.async (generic proxy)
           const uint32_t st = smem_u32(stage_base + (size_t)s * stage_bytes);
           const uint64_t bdesc = umma_desc_sw128(st + MT * kAStageBytes);
 #pragma unroll
@@ -400,15 +445,25 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
           break;
         }
         const int n0 = tile_n0(i) + row0, kb = i % num_kb;
+        if constexpr (COPY && BITS != 0) {
 #pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-          const int rr = lane + 32 * r;
-          if (r == 0 ? rr < rows_per_warp : (two && rr < rows_per_warp))
-            emit_row<T, BITS>(cur[r], p, n0 + rr, kb, b_stage, row0 + rr, res_tab);
+          for (int r = 0; r < RPL; ++r) {
+            const int rr = lane + 32 * r;
+            if (r == 0 ? rr < rows_per_warp : (two && rr < rows_per_warp))
+              emit_row_copy<BITS>(cur[r], p, n0 + rr < p.N, kb, b_stage, row0 + rr);
+          }
+          cp_async_arrive(&full_bar[grp]);  // every lane, also one without rows
+        } else {
+#pragma unroll
+          for (int r = 0; r < RPL; ++r) {
+            const int rr = lane + 32 * r;
+            if (r == 0 ? rr < rows_per_warp : (two && rr < rows_per_warp))
+              emit_row<T, BITS>(cur[r], p, n0 + rr, kb, b_stage, row0 + rr, res_tab);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_bar[grp]);
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_bar[grp]);
 #pragma unroll
         for (int r = 0; r < RPL; ++r) cur[r] = nxt[r];
       }
@@ -420,12 +475,20 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);  // let issued TMA copies land
   }
+  if (COPY) asm volatile("cp.async.wait_all;" ::: "memory");  // none of this thread's copies outlives the CTA
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
+}
+
+// out[i] = T(in[i]): the cast the decode applies to a plain weight's codebook entries.
+template <typename T>
+__global__ void codebook_cast_kernel(const __half* __restrict__ in, T* __restrict__ out, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_half<T>(in[i]);
 }
 
 // BN: a multiple of 16 in [16, 256] such that (waves of tiles) x BN -- the decode work of the
@@ -473,9 +536,9 @@ int make_tmap_x(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, 
   return NPB_OK;
 }
 
-template <typename T, int MT, int BITS>
+template <typename T, int MT, int BITS, bool COPY>
 int launch(const void* x, FusedParams p, cudaStream_t st) {
-  auto kern = vq_gemm_fused_kernel<T, MT, BITS>;
+  auto kern = vq_gemm_fused_kernel<T, MT, BITS, COPY>;
   const int sms = sm_count();
   p.tiles_m = (p.M + BM * MT - 1) / (BM * MT);
   p.BN = pick_bn(p.N, p.tiles_m, MT, sms);
@@ -512,9 +575,16 @@ int launch(const void* x, FusedParams p, cudaStream_t st) {
 
 template <typename T, int BITS>
 int launch_mt(const void* x, const FusedParams& p, cudaStream_t st) {
-  if (p.M <= 128) return launch<T, 1, BITS>(x, p, st);
-  if (p.M <= 256) return launch<T, 2, BITS>(x, p, st);
-  return launch<T, 3, BITS>(x, p, st);
+  if constexpr (BITS != 0) {
+    if (p.cb_x != nullptr) {
+      if (p.M <= 128) return launch<T, 1, BITS, true>(x, p, st);
+      if (p.M <= 256) return launch<T, 2, BITS, true>(x, p, st);
+      return launch<T, 3, BITS, true>(x, p, st);
+    }
+  }
+  if (p.M <= 128) return launch<T, 1, BITS, false>(x, p, st);
+  if (p.M <= 256) return launch<T, 2, BITS, false>(x, p, st);
+  return launch<T, 3, BITS, false>(x, p, st);
 }
 
 template <typename T>
@@ -542,8 +612,24 @@ int vq_gemm_fused_device_status(int* host_out) {
   return NPB_OK;
 }
 
-int vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
-                  const float* bias, void* y, cudaStream_t st) {
+int vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int out_dtype, cudaStream_t st) {
+  if (n_values < 0) return NPB_ERR_INVALID_ARG;
+  if (out_dtype != NPB_BF16 && out_dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
+  if (n_values == 0) return NPB_OK;
+  if (centroids == nullptr || out == nullptr) return NPB_ERR_INVALID_ARG;
+  const unsigned blocks = (unsigned)((n_values + 255) / 256);
+  const __half* in = static_cast<const __half*>(centroids);
+  if (out_dtype == NPB_BF16)
+    codebook_cast_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(in, static_cast<__nv_bfloat16*>(out), n_values);
+  else
+    codebook_cast_kernel<__half><<<blocks, 256, 0, st>>>(in, static_cast<__half*>(out), n_values);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+// codebook_x: null, or the codebook in the activation type (vq_codebook_cast) for the copy form.
+int vq_gemm_fused(const npb_vq_weight* w, const void* codebook_x, const void* x, int x_dtype, int64_t M, int64_t N,
+                  int64_t K, const float* bias, void* y, cudaStream_t st) {
   if (int rc = validate_vq(w, N, K)) return rc;
   if (M < 0) return NPB_ERR_INVALID_ARG;
   if (x_dtype != NPB_BF16 && x_dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
@@ -583,6 +669,13 @@ int vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_t M,
       (p.groups_per_codebook % 8 == 0) && (!p.has_res || (w->res_bits == 8 && aligned_to(w->res_packed, 8))))
     vbits = w->bits;
   if (vbits == 0 && p.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
+  if (codebook_x != nullptr) {
+    // the copy form covers plain weights with wide index reads; anything else is the caller's mistake
+    if (p.has_res || p.has_scale || vbits == 0) return NPB_ERR_UNSUPPORTED;
+    if (!aligned_to(codebook_x, 16)) return NPB_ERR_ALIGNMENT;
+    p.cb_x = codebook_x;
+    p.clamp = (w->num_centroids != (1 << w->bits)) || p.groups_per_codebook > 0;
+  }
   return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(x, p, vbits, st) : launch_bits<__half>(x, p, vbits, st);
 }
 

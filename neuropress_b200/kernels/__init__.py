@@ -204,7 +204,67 @@ def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torc
     """Tile-decode tensor-core GEMM (tcgen05): same signature as the reference's
     ``vq_gemm_triton`` (vq_triton.py:119-179).  bf16 / fp16 activations, vector length 8,
     ``K % 64 == 0``."""
+    ext_n = _vq_ext(ext)
+    if (VQ_COPY_FORM and ext_n.get("residual_indices") is None and ext_n.get("row_scale") is None
+            and bits in (8, 12, 16) and centroids.shape[-1] == 8 and x.dim() == 2
+            and x.dtype in (torch.float16, torch.bfloat16) and packed_indices.data_ptr() % 16 == 0):
+        y = _vq_gemm_fused_copy(x, packed_indices, centroids, bits, out_features, bias, ext_n)
+        if y is not None:
+            return y
     return _vq_call("npb_vq_gemm_fused", x, packed_indices, centroids, bits, out_features, bias, ext)
+
+
+# Plain weights take the copy form of the tile-decode GEMM (``npb_vq_gemm_fused_cb``): the codebook
+# is cast once to the activation type and the kernel copies entries instead of converting them.
+VQ_COPY_FORM = True
+_cast_codebooks: dict = {}   # id(centroids) -> (weakref to it, its version, {dtype: cast tensor})
+
+
+def codebook_in_dtype(centroids: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``centroids`` (fp16 codebook) cast to ``dtype`` by ``npb_vq_codebook_cast``, cached per
+    codebook tensor (dropped when the tensor dies or is modified in place).  fp16 returns the
+    codebook itself."""
+    if dtype == torch.float16:
+        return centroids
+    import weakref
+    key = id(centroids)
+    hit = _cast_codebooks.get(key)
+    if hit is not None and hit[0]() is centroids and hit[1] == centroids._version and dtype in hit[2]:
+        return hit[2][dtype]
+    _cabi.require_cuda("vq_codebook_cast", centroids)
+    lib = _cabi.load_library()
+    out = torch.empty(centroids.shape, dtype=dtype, device=centroids.device)
+    with torch.cuda.device(centroids.device):
+        rc = _launch("npb_vq_codebook_cast", lib.npb_vq_codebook_cast, centroids.data_ptr(), centroids.numel(),
+                     out.data_ptr(), _cabi.dtype_code(dtype), _cabi.stream_ptr())
+    _cabi.check(rc, "npb_vq_codebook_cast")
+    if hit is None or hit[0]() is not centroids or hit[1] != centroids._version:
+        ref = weakref.ref(centroids, lambda _r, k=key: _cast_codebooks.pop(k, None))
+        hit = (ref, centroids._version, {})
+        _cast_codebooks[key] = hit
+    hit[2][dtype] = out
+    return out
+
+
+def _vq_gemm_fused_copy(x, packed, centroids, bits, out_features, bias, ext):
+    _cabi.require_cuda("npb_vq_gemm_fused_cb", x, packed, centroids)
+    if not centroids.is_contiguous() or centroids.dtype != torch.float16:
+        raise RuntimeError("vq_gemm_fused: the codebook must be a contiguous fp16 tensor.")
+    lib = _cabi.load_library()
+    m, k = x.shape
+    n = out_features if out_features is not None else _infer_n(packed, bits, k, 8)
+    cbx = codebook_in_dtype(centroids, x.dtype)
+    w = _cabi.vq_struct(packed, centroids, bits, **ext)
+    b = _bias_f32(bias, n, x.device)
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _launch("npb_vq_gemm_fused", lib.npb_vq_gemm_fused_cb, w, cbx.data_ptr(), x.data_ptr(),
+                     _cabi.dtype_code(x.dtype), m, n, k, None if b is None else b.data_ptr(), y.data_ptr(),
+                     _cabi.stream_ptr())
+    if rc == 2:   # NPB_ERR_UNSUPPORTED: this weight needs the converting form
+        return None
+    _cabi.check(rc, "npb_vq_gemm_fused_cb")
+    return y
 
 
 # Whether the mid-sized band runs the tile-decode GEMM (``npb_vq_gemm_fused``); when False it

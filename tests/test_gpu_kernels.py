@@ -275,6 +275,48 @@ def test_vq_gemm_fused_matches_oracle(case, dtype, rows):
     assert_output_close(y, _vq_forward_ref64(layer, x), dtype, tol=2e-3)
 
 
+COPY_CASES = [  # N, K, NC, bits, cols_per_codebook: plain weights (the copy form's domain)
+    (256, 512, 4096, 16, 0),      # indices above the codebook size are clamped
+    (200, 1024, 4096, 12, 0),     # N tail, 12-bit stream
+    (1000, 2048, 65536, 16, 0),   # full 16-bit codebook: no clamp
+    (128, 2048, 4096, 16, 512),   # one codebook per 512 columns
+    (130, 256, 256, 8, 0),
+    (4096, 8192, 65536, 16, 0),   # many tiles per CTA: every ring stage wraps
+]
+
+
+@pytest.mark.parametrize("case", COPY_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows", [17, 32, 130, 300])
+def test_vq_gemm_fused_copy_form_equals_converting_form(case, dtype, rows, monkeypatch):
+    """Plain weights take the asynchronous-copy form of the tile-decode GEMM (codebook cast once,
+    entries copied into the operand tile).  It must give the converting form's bits."""
+    from neuropress_b200 import _cabi
+    N, K, NC, bits, cpc = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + K + bits, cols_per_codebook=cpc, bias=True)
+    x = make_activations(rows, K, dtype, seed=rows).to(DEV)
+    args = (x, layer.packed.to(DEV), layer.centroids.to(DEV), bits, N, layer.bias.to(DEV))
+    ext = _vq_ext_gpu(layer)
+    monkeypatch.setattr(kernels, "VQ_COPY_FORM", True)
+    y_copy = kernels.vq_gemm_fused(*args, **ext)
+    assert _cabi.gemm_device_status() == 0
+    monkeypatch.setattr(kernels, "VQ_COPY_FORM", False)
+    y_conv = kernels.vq_gemm_fused(*args, **ext)
+    assert _cabi.gemm_device_status() == 0
+    assert torch.equal(y_copy, y_conv)
+    if N <= 1000:
+        assert_output_close(y_copy, _vq_forward_ref64(layer, x.cpu()), dtype, tol=2e-3)
+
+
+def test_vq_codebook_cast_matches_torch():
+    c = (torch.randn(4096, 8, generator=torch.Generator().manual_seed(3)) * 0.02).half().to(DEV)
+    assert torch.equal(kernels.codebook_in_dtype(c, torch.bfloat16), c.to(torch.bfloat16))
+    assert kernels.codebook_in_dtype(c, torch.bfloat16) is kernels.codebook_in_dtype(c, torch.bfloat16)  # cached
+    assert kernels.codebook_in_dtype(c, torch.float16) is c
+    c.mul_(2)  # an in-place change invalidates the cached table
+    assert torch.equal(kernels.codebook_in_dtype(c, torch.bfloat16), c.to(torch.bfloat16))
+
+
 @pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rows", [9, 130, 384])
