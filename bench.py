@@ -242,7 +242,7 @@ def graph_time_ms(calls, reps: int = 1) -> float:
 class C5:
     """The headline workload: N_COPIES copies of the 7-linear set, this rank's shards only."""
 
-    def __init__(self, device, rank: int, world: int, nccl_gather: bool) -> None:
+    def __init__(self, device, rank: int, world: int, nccl_gather: bool, decode_ahead: bool = False) -> None:
         from neuropress_b200.nn import NPVQLinear, VQProxy
         from neuropress_b200.sharding import ShardedLinear
 
@@ -265,6 +265,11 @@ class C5:
                 del full, packed
             self.copies.append(layers)
         torch.cuda.empty_cache()
+        # the next linear's weight is decoded on a side stream under the current linear's GEMM
+        from neuropress_b200.nn import DecodeAhead
+
+        self.ahead = [DecodeAhead([layers[name] for name, _, _ in C5_LINEARS], torch.bfloat16)
+                      for layers in self.copies] if decode_ahead else []
         self.x = {rows: {key: device_normal((rows, w), device, 7 + rows + 13 * i)
                          for i, (key, w) in enumerate(C5_INPUT_WIDTH.items())} for rows in C5_ROWS}
         self.gather_kind = "none"
@@ -308,6 +313,13 @@ class C5:
                 y = layers[name](xs[rows][C5_INPUT[name]])
                 if sink is not None:
                     sink(name, rows, y)
+            if self.ahead:
+                self.ahead[c % N_COPIES].join()   # the side stream rejoins before the next part of the pass
+
+    def set_decode_ahead(self, on: bool) -> None:
+        for a in self.ahead:
+            a.join()
+            a.enabled = on
 
     def local_cols(self, name: str, n: int) -> tuple[int, int]:
         if not self.sharded[name]:
@@ -405,7 +417,8 @@ def run_ours(args) -> dict:
             os.dup2(saved, 1)
             os.close(saved)
 
-    wl = C5(device, rank, world, args.nccl_gather)
+    wl = C5(device, rank, world, args.nccl_gather, args.decode_ahead)
+    wl.set_decode_ahead(args.decode_ahead)
     steps, warmup = args.steps, max(args.warmup, 3)
     tokens_per_step = TOKENS_PER_PASS * PASSES_PER_STEP
 
@@ -545,9 +558,11 @@ def run_ours(args) -> dict:
     kernels.set_launch_hook(timer)
     timer.count = 0
     barrier()
-    for q in range(2):                                   # per-launch device times, two eager passes
+    wl.set_decode_ahead(False)                           # per-launch device times: two eager passes,
+    for q in range(2):                                   # one kernel at a time
         wl.run_pass(q, timer=timer)
     barrier()
+    wl.set_decode_ahead(args.decode_ahead)
     eager_launches_per_pass = timer.count // 2
     kernels.set_launch_hook(None)
     with ClockSampler(local_rank) as clocks_e2e:
@@ -566,8 +581,13 @@ def run_ours(args) -> dict:
         "ms_per_step": round(total_ms / steps, 4), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": c5_config(world, wl.gather_kind,
-                            "CUDA-graph replay of the 14 module forwards of a pass (one graph per copy of "
-                            "the layer set)" if graphs else "eager module forwards"),
+                            ("CUDA-graph replay of the 14 module forwards of a pass (one graph per copy of "
+                             "the layer set)" if graphs else "eager module forwards")
+                            + ("" if not args.decode_ahead else
+                               "; in the 4096-row part the next linear's weight is decoded on a side stream "
+                               "under the current linear's GEMM (nn.DecodeAhead)")),
+        "kernel_timing": "pass_kernel_ms and the rooflines: two eager passes with one CUDA-event pair per "
+                         "launch, kernels one at a time (decode-ahead off)",
         "timed_region_s": round(total_ms * 1e-3, 3),
         "ms_per_pass": round(total_ms / steps / PASSES_PER_STEP, 4),
         "e2e": {"value": round(tokens_per_step * steps / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
@@ -583,6 +603,9 @@ def run_ours(args) -> dict:
     line.update(c5_rooflines(kmean, world, wl, peaks, peak_src, total_ms / steps / PASSES_PER_STEP))
     if world == 1 and not args.no_extras:
         del graphs
+        for a in wl.ahead:
+            a.close()
+        wl.ahead.clear()
         wl.copies.clear()
         torch.cuda.empty_cache()
         for key, fn in (("c2", lambda: run_c2(device, peaks, peak_src)),
@@ -1206,6 +1229,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="N = 1: skip the c2 / c3 / c4 / probe tables")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replay")
+    ap.add_argument("--decode-ahead", action="store_true",
+                    help="decode the next linear's weight on a side stream under the current linear's GEMM "
+                         "(nn.DecodeAhead); measured neutral under the sustained power cap, so off by default")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="N > 1: all-gather with NCCL instead of the peer-store epilogues")
     args = ap.parse_args()

@@ -69,6 +69,30 @@ typedef struct {
 } npb_vq_weight;
 
 /*
+ * An entropy-coded index stream in one of the reference's three wire formats
+ * (neuropress/transforms/vq_packing.py: TieredIndexPacking :298-610, NTieredIndexPacking
+ * :612-1034, ZeroEscapePacking :1037-1384), described by where its sub-streams sit:
+ *   kind 1: n_tiers - 1 cascaded one-bit prefix streams (prefix k has one bit per index not in a
+ *           tier < k: 0 = tier k, 1 = later); two-tier and N-tier buffers.
+ *   kind 2: one two-bit prefix per index = its tier (zero escape: n_tiers = 4, tier 0 = centroid
+ *           0 without payload).
+ * Index value = tier_lo[t] + the tier_bits[t]-bit payload at the index's rank in tier t's stream.
+ * row_off[t][n] = number of tier-t indices in rows < n (device int32 [N + 1], the packers'
+ * compute_row_offsets).  Offsets are bytes from buf.
+ */
+typedef struct {
+  const uint8_t* buf;           /* the whole coded buffer (header included), 4-byte aligned   */
+  int64_t buf_bytes;
+  int32_t kind;                 /* 1 or 2                                                     */
+  int32_t n_tiers;              /* 2..4                                                       */
+  int64_t prefix_off[3];        /* kind 1: prefix stream k, k < n_tiers - 1; kind 2: [0]      */
+  int64_t tier_off[4];          /* payload stream of tier t                                   */
+  int32_t tier_bits[4];         /* 0..20 (0: no payload)                                      */
+  int32_t tier_lo[4];
+  const int32_t* row_off[4];
+} npb_vq_entropy_stream;
+
+/*
  * One group-affine weight matrix W[N, K] = (q - zp) * scale, fp32 arithmetic, cast to the
  * activation dtype (neuropress/nn/np_linear.py:298-353; kernel q4_linear.cu:80-131).
  * zero_point == NULL means the symmetric scheme with zp = 2^(nbits-1).
@@ -165,6 +189,15 @@ int npb_vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int
 int npb_vq_gemm_fused_cb(const npb_vq_weight* w, const void* codebook_x, const void* x, int x_dtype,
                          int64_t M, int64_t N, int64_t K, const float* bias, void* y,
                          npb_stream_t stream);
+
+/* Expands an entropy-coded index stream of N rows x G indices into the plain little-endian
+ * uint16 index table [N, G] (= an IndexPacking stream with bits = 16) that every other entry
+ * point takes, so each row-count band serves entropy-coded layers: expand, then the band's
+ * kernel.  One warp per row; bit-exact against the packers' unpack().  Values above 65535 are
+ * stored as 65535.  Stands in for the index decoding inside the reference's tiered GEMV kernels
+ * (neuropress/kernels/vq_linear_tiered.cu, vq_linear_ntier.cu, vq_linear_zero_escape.cu). */
+int npb_vq_entropy_expand(const npb_vq_entropy_stream* s, int64_t N, int64_t G, void* out_u16,
+                          npb_stream_t stream);
 
 /* Same for group-affine weights (no reference counterpart beyond q_linear, which re-reads
  * the weight per row: neuropress/kernels/q4_linear.cu:80-131). nbits 4, K % 64 == 0,

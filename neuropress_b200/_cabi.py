@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "npb_vq_gemm_fused",
     "npb_vq_gemm_fused_cb",
     "npb_vq_codebook_cast",
+    "npb_vq_entropy_expand",
     "npb_q_gemm_fused",
     "npb_vq_linear_static_scratch",
     "npb_allgather_push",
@@ -52,6 +53,16 @@ EXPORTED_SYMBOLS = (
     "npb_set_gemm_pair_mode",
     "npb_get_gemm_pair_mode",
 )
+
+
+class EntropyStreamStruct(Structure):
+    """Mirror of ``npb_vq_entropy_stream``."""
+
+    _fields_ = [
+        ("buf", c_void_p), ("buf_bytes", c_int64), ("kind", c_int32), ("n_tiers", c_int32),
+        ("prefix_off", c_int64 * 3), ("tier_off", c_int64 * 4), ("tier_bits", c_int32 * 4),
+        ("tier_lo", c_int32 * 4), ("row_off", c_void_p * 4),
+    ]
 
 
 class VQWeightStruct(Structure):
@@ -137,6 +148,7 @@ def load_library() -> ctypes.CDLL:
     lib.npb_vq_gemm_fused.argtypes = [vq_p, *gemv_tail]
     lib.npb_vq_gemm_fused_cb.argtypes = [vq_p, c_void_p, *gemv_tail]
     lib.npb_vq_codebook_cast.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_void_p]
+    lib.npb_vq_entropy_expand.argtypes = [POINTER(EntropyStreamStruct), c_int64, c_int64, c_void_p, c_void_p]
     lib.npb_vq_linear_static_scratch.argtypes = [vq_p, *gemv_tail]
     lib.npb_q_gemm_fused.argtypes = [q_p, *gemv_tail]
     lib.npb_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

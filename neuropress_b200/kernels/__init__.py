@@ -273,6 +273,41 @@ VQ_TILE_DECODE_GEMM = True
 VQ_FUSED_MAX_ROWS = 384   # above this every weight tile would be decoded more than three times
 
 
+def vq_entropy_expand(packed: torch.Tensor, layout: dict, row_offsets: list[torch.Tensor], n_rows: int,
+                      n_groups: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Expand an entropy-coded index buffer (``TieredIndexPacking`` / ``NTieredIndexPacking`` /
+    ``ZeroEscapePacking``) into the plain 16-bit index stream: a 1-D ``uint8`` tensor of
+    ``n_rows * n_groups * 2`` bytes, i.e. what ``IndexPacking.pack(indices, 16)`` gives.
+    ``layout`` is ``transforms.entropy_packing.describe_entropy_buffer(packed, scheme)``,
+    ``row_offsets`` the packer's ``compute_row_offsets`` as int32 tensors on the device of
+    ``packed``, one per tier.  Stands in for the index decoding of the reference's
+    ``vq_linear_tiered`` / ``vq_linear_ntier`` / ``vq_linear_zero_escape`` kernels."""
+    _cabi.require_cuda("vq_entropy_expand", packed, *row_offsets)
+    lib = _cabi.load_library()
+    n_tiers = len(layout["bits"])
+    if len(row_offsets) != n_tiers or layout["n"] != n_rows * n_groups:
+        raise RuntimeError("vq_entropy_expand: row offsets / sizes do not match the buffer's header.")
+    for off in row_offsets:
+        if off.dtype != torch.int32 or off.numel() != n_rows + 1 or not off.is_contiguous():
+            raise RuntimeError("vq_entropy_expand: row offsets must be contiguous int32 [n_rows + 1].")
+    s = _cabi.EntropyStreamStruct()
+    s.buf, s.buf_bytes, s.kind, s.n_tiers = packed.data_ptr(), packed.numel(), layout["kind"], n_tiers
+    for k, v in enumerate(layout["prefix_off"]):
+        s.prefix_off[k] = v
+    for k in range(n_tiers):
+        s.tier_off[k], s.tier_bits[k], s.tier_lo[k] = layout["tier_off"][k], layout["bits"][k], layout["lo"][k]
+        s.row_off[k] = row_offsets[k].data_ptr()
+    if out is None:
+        out = torch.empty(n_rows * n_groups * 2, dtype=torch.uint8, device=packed.device)
+    elif out.dtype != torch.uint8 or out.numel() != n_rows * n_groups * 2 or not out.is_contiguous():
+        raise RuntimeError("vq_entropy_expand: `out` must be a contiguous uint8 tensor of 2 bytes per index.")
+    with torch.cuda.device(packed.device):
+        rc = _launch("npb_vq_entropy_expand", lib.npb_vq_entropy_expand, ctypes.byref(s), n_rows, n_groups,
+                     out.data_ptr(), _cabi.stream_ptr())
+    _cabi.check(rc, "vq_entropy_expand")
+    return out
+
+
 def vq_dequant_gemm(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
                     bits: int, out_features: int | None = None, bias: torch.Tensor | None = None,
                     **ext) -> torch.Tensor:

@@ -32,7 +32,8 @@ class LinearGroup:
     def __init__(self, members: list[NPVQLinear], norm: NPRMSNorm | None = None) -> None:
         first = members[0]
         for m in members:
-            if not isinstance(m, NPVQLinear) or m.in_features != first.in_features or m.bits != first.bits \
+            if not isinstance(m, NPVQLinear) or m._entropy_scheme is not None \
+                    or m.in_features != first.in_features or m.bits != first.bits \
                     or m.vector_len != first.vector_len or m.cols_per_codebook != first.cols_per_codebook \
                     or m.proxy.num_centroids != first.proxy.num_centroids:
                 raise ValueError("grouped linears must be NPVQLinear modules of one input width, index width "

@@ -59,8 +59,8 @@ _SMALL_BATCH_MAX_TOKENS: int = int(os.environ.get("NEUROPRESS_B200_VQ_SMALL_BATC
 _LUT_SKIPS_TILE_BAND: bool = False
 
 _FUSED_BACKENDS = frozenset({VQBackend.CUDA_WMMA, VQBackend.CUDA_LUT, VQBackend.CUDA})
-_UNIMPLEMENTED = frozenset({VQBackend.DEFAULT, VQBackend.COMPILE, VQBackend.CUDA_TIERED,
-                            VQBackend.CUDA_NTIER, VQBackend.CUDA_ZERO_ESCAPE})
+_ENTROPY_BACKENDS = frozenset({VQBackend.CUDA_TIERED, VQBackend.CUDA_NTIER, VQBackend.CUDA_ZERO_ESCAPE})
+_UNIMPLEMENTED = frozenset({VQBackend.DEFAULT, VQBackend.COMPILE})
 
 
 def _fused_max_tokens(backend: VQBackend) -> int:
@@ -148,10 +148,16 @@ class VQProxy(nn.Module):
 class NPVQLinear(nn.Module):
     """Linear layer whose weight is packed VQ indices plus a shared :class:`VQProxy`.
 
-    Constructor arguments follow the reference (:493-513); the entropy-coded ones
-    (``use_tiered`` ... ``zesc_row_offsets``) are accepted and stored but their kernels are not
-    part of this package.  Keyword-only extensions: ``residual_proxy``, ``residual_indices``,
-    ``residual_bits``, ``row_scale``, ``cols_per_codebook``.
+    Constructor arguments follow the reference (:493-513).  With ``use_tiered``, ``tier_bits`` or
+    ``zero_escape`` the ``packed_indices`` buffer holds an entropy-coded stream
+    (``TieredIndexPacking`` / ``NTieredIndexPacking`` / ``ZeroEscapePacking``) and the per-row
+    offsets are buffers named as in the reference (``hot_row_offsets``, ``cold_row_offsets``,
+    ``ntier_row_off_{k}``, ``zesc_row_off_{k}``; computed here when not passed).  Such a layer
+    expands its stream to plain 16-bit indices on the GPU at every forward
+    (``npb_vq_entropy_expand``) and then takes the same row-count bands as a plain layer; the
+    coded buffer stays whole (the reference splits it into per-stream buffers, :644-801).
+    Keyword-only extensions: ``residual_proxy``, ``residual_indices``, ``residual_bits``,
+    ``row_scale``, ``cols_per_codebook``.
     """
 
     def __init__(
@@ -236,6 +242,55 @@ class NPVQLinear(nn.Module):
             raise ValueError("row_scale must have out_features elements.")
         self._bias_f32: torch.Tensor | None = None
         self._bias_key = None
+        self._entropy_scheme: str | None = None
+        self._entropy_layout: dict | None = None
+        self._decode_ahead = None   # a decode_ahead.DecodeAhead that prefetches this layer's dense weight
+        if zero_escape or tier_bits is not None or use_tiered:
+            self._init_entropy(hot_row_offsets, cold_row_offsets, ntier_row_offsets, zesc_row_offsets)
+
+    def _init_entropy(self, hot, cold, ntier, zesc) -> None:
+        """Row-offset buffers (reference names, :604-625) and the host-side description of where
+        the coded buffer's sub-streams sit; offsets that were not passed are computed by the
+        packers, as ``from_qtensor_linear`` does in the reference (:878-895)."""
+        from ..transforms.entropy_packing import (NTieredIndexPacking, TieredIndexPacking, ZeroEscapePacking,
+                                                  describe_entropy_buffer)
+
+        groups = self.in_features // self.vector_len
+        if self.zero_escape:
+            scheme, names = "zero_escape", [f"zesc_row_off_{i}" for i in range(4)]
+            offs = zesc if zesc is not None else ZeroEscapePacking.compute_row_offsets(
+                self.packed_indices, self.out_features, groups)
+        elif self.tier_bits is not None:
+            scheme, names = "ntier", [f"ntier_row_off_{i}" for i in range(len(self.tier_bits))]
+            offs = ntier if ntier is not None else NTieredIndexPacking.compute_row_offsets(
+                self.packed_indices, self.out_features, groups)
+        else:
+            scheme, names = "tiered", ["hot_row_offsets", "cold_row_offsets"]
+            offs = [hot, cold] if hot is not None and cold is not None else list(
+                TieredIndexPacking.compute_row_offsets(self.packed_indices, self.out_features, groups))
+        layout = describe_entropy_buffer(self.packed_indices, scheme)
+        if len(offs) != len(names) or len(layout["bits"]) != len(names):
+            raise ValueError("row offsets do not match the coded buffer's tiers.")
+        if layout["n"] != self.n_vectors:
+            raise ValueError(f"coded buffer holds {layout['n']} indices, the layer needs {self.n_vectors}.")
+        if max(layout["bits"]) > 16 or self.proxy.num_centroids > 65536:
+            raise ValueError("entropy-coded layers are expanded to 16-bit indices: tiers wider than 16 bits "
+                             "and codebooks beyond 65536 entries are not supported.")
+        for name, off in zip(names, offs):
+            self.register_buffer(name, off.to(device=self.packed_indices.device, dtype=torch.int32).contiguous())
+        self._entropy_scheme, self._entropy_layout, self._entropy_names = scheme, layout, names
+
+    def _stream(self) -> tuple[torch.Tensor, int]:
+        """The plain index stream the band kernels read and its width: the ``packed_indices``
+        buffer itself, or, for an entropy-coded layer, its expansion to 16-bit indices."""
+        if self._entropy_scheme is None:
+            return self.packed_indices, self.bits
+        from .. import kernels
+
+        plain = kernels.vq_entropy_expand(self.packed_indices, self._entropy_layout,
+                                          [getattr(self, n) for n in self._entropy_names], self.out_features,
+                                          self.in_features // self.vector_len)
+        return plain, 16
 
     # ------------------------------------------------------------------ factory / serde
     @classmethod
@@ -252,9 +307,6 @@ class NPVQLinear(nn.Module):
         qscheme = getattr(weight_q, "qscheme", None)
         if qscheme is None or not hasattr(qscheme, "centroids") or not hasattr(weight_q, "u8_blob"):
             raise TypeError(f"Expected a VQ QTensor weight, got {type(weight_q).__name__!r}.")
-        if getattr(qscheme, "use_tiered", False) or getattr(qscheme, "tier_bits", None) is not None \
-                or getattr(qscheme, "zero_escape", False):
-            raise ValueError("entropy-coded index streams are not supported by this package.")
         bias = linear.bias.detach().clone() if linear.bias is not None else None
         perm = getattr(qscheme, "column_permutation", None)
         meta = weight_q.serde_metadata() if hasattr(weight_q, "serde_metadata") else {}
@@ -268,7 +320,11 @@ class NPVQLinear(nn.Module):
             backend=backend,
             bias=bias,
             column_perm=None if perm is None else perm.detach().clone(),
+            use_tiered=bool(getattr(qscheme, "use_tiered", False)),
+            cold_bits=qscheme.is_packed_indices,
             qtensor_meta=meta,
+            tier_bits=getattr(qscheme, "tier_bits", None),
+            zero_escape=bool(getattr(qscheme, "zero_escape", False)),
         )
 
     def to_qtensor(self):
@@ -285,6 +341,7 @@ class NPVQLinear(nn.Module):
 
         scheme = VQScheme(centroids=self.proxy.centroids, vector_len=self.vector_len,
                           is_packed_indices=self.bits, column_permutation=self.column_perm,
+                          use_tiered=self.use_tiered, tier_bits=self.tier_bits, zero_escape=self.zero_escape,
                           original_shape=(self.out_features, self.in_features))
         meta = {k: v for k, v in self._qtensor_meta.items() if k not in ("type", "shape")}
         return VQQTensor(u8_blob=self.packed_indices, qscheme=scheme,
@@ -300,7 +357,10 @@ class NPVQLinear(nn.Module):
         otherwise the local result is pushed by a separate kernel."""
         if self.column_perm is not None:
             x = x[..., self.column_perm]
-        if self.backend in _FUSED_BACKENDS:
+        if self.backend in _ENTROPY_BACKENDS and self._entropy_scheme is None:
+            raise RuntimeError(f"backend {self.backend.value!r} needs an entropy-coded packed_indices buffer "
+                               "(use_tiered / tier_bits / zero_escape).")
+        if self.backend in _FUSED_BACKENDS or self.backend in _ENTROPY_BACKENDS:
             m = x.numel() // self.in_features
             if m > _fused_max_tokens(self.backend):
                 if m <= _SMALL_BATCH_MAX_TOKENS and self._small_batch_ok(x, m):
@@ -313,12 +373,11 @@ class NPVQLinear(nn.Module):
             return self._forward_cuda_lut(x, gather)
         if self.backend == VQBackend.CUDA_WMMA:
             return self._forward_cuda_wmma(x, gather)
-        if self.backend == VQBackend.CUDA:
+        if self.backend == VQBackend.CUDA or self.backend in _ENTROPY_BACKENDS:
             return self._forward_cuda(x, gather)
         raise NotImplementedError(
             f"backend {self.backend.value!r} is not implemented by this package: only the CUDA "
-            "backends (cuda, cuda_wmma, cuda_lut) exist here; there is no eager, compiled or "
-            "entropy-coded path."
+            "backends exist here; there is no eager or compiled path."
         )
 
     # -- helpers
@@ -361,7 +420,8 @@ class NPVQLinear(nn.Module):
         k = self.in_features
         if x.dtype not in (torch.bfloat16, torch.float16) or self.vector_len != 8:
             return False
-        if self.bits not in (8, 12, 16) or k % 1024 or k > (4096 if m > 8 else 8192):
+        bits = 16 if self._entropy_scheme is not None else self.bits
+        if bits not in (8, 12, 16) or k % 1024 or k > (4096 if m > 8 else 8192):
             return False
         if self.cols_per_codebook and self.cols_per_codebook % 256:
             return False
@@ -376,7 +436,8 @@ class NPVQLinear(nn.Module):
 
         x2, leading = self._flat(x)
         fused = gather is not None and gather.accepts(x2.shape[0], x2.dtype)
-        y = kernels.vq_gemv(x2, self.packed_indices, self.proxy.centroids, self.bits,
+        packed, bits = self._stream()
+        y = kernels.vq_gemv(x2, packed, self.proxy.centroids, bits,
                             self.out_features, self._bias32(), gather=gather if fused else None,
                             **self._ext())
         if gather is not None and not fused:
@@ -411,7 +472,8 @@ class NPVQLinear(nn.Module):
                 or (self.residual_indices is not None and self.residual_proxy.num_centroids > 256)):
             return self._forward_dequant_gemm(x, gather)
         x2, leading = self._flat(x)
-        y = kernels.vq_gemm_fused(x2, self.packed_indices, self.proxy.centroids, self.bits,
+        packed, bits = self._stream()
+        y = kernels.vq_gemm_fused(x2, packed, self.proxy.centroids, bits,
                                   self.out_features, self._bias32(), **self._ext())
         if gather is not None:
             y = gather(y)
@@ -428,14 +490,28 @@ class NPVQLinear(nn.Module):
         if orig == torch.float32:
             x = x.to(torch.float16)
         x2, leading = self._flat(x)
-        w = kernels.vq_dequant(self.packed_indices, self.proxy.centroids, self.bits,
-                               self.out_features, self.in_features, x2.dtype, **self._ext())
+        ahead = self._decode_ahead
+        w = ahead.weight_for(self, x2.dtype) if ahead is not None else None
+        if w is None:
+            ahead = None
+            w = self._decode_dense(x2.dtype)
         fused = gather is not None and orig == x2.dtype and gather.accepts(x2.shape[0], x2.dtype)
         y = kernels.gemm(x2, w, self._bias32(), gather=gather if fused else None)
+        if ahead is not None:
+            ahead.release(self)
         y = y.to(orig) if y.dtype != orig else y
         if gather is not None and not fused:
             y = gather(y)
         return y.reshape(*leading, y.shape[-1])
+
+    def _decode_dense(self, dtype: torch.dtype, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The whole weight as a dense ``[N, K]`` matrix of ``dtype`` on the current stream (an
+        entropy-coded stream is expanded first)."""
+        from .. import kernels
+
+        packed, bits = self._stream()
+        return kernels.vq_dequant(packed, self.proxy.centroids, bits, self.out_features, self.in_features,
+                                  dtype, out=out, **self._ext())
 
     def extra_repr(self) -> str:
         perm = ", perm=True" if self.column_perm is not None else ""
@@ -446,6 +522,8 @@ class NPVQLinear(nn.Module):
             ext += ", row_scale=True"
         if self.cols_per_codebook:
             ext += f", cols_per_codebook={self.cols_per_codebook}"
+        if self._entropy_scheme is not None:
+            ext += f", index_stream={self._entropy_scheme}"
         return (f"in={self.in_features}, out={self.out_features}, vector_len={self.vector_len}, "
                 f"num_centroids={self.proxy.num_centroids}, bits={self.bits}, "
                 f"backend={self.backend.value}{perm}{ext}")

@@ -42,6 +42,9 @@ def _stream_slice(packed: torch.Tensor, bits: int, groups: int, begin: int, end:
 
 def shard_vq_linear(layer: NPVQLinear, world_size: int, rank: int) -> NPVQLinear:
     """The rows of *layer* that *rank* owns, as a new :class:`NPVQLinear` sharing its proxies."""
+    if layer._entropy_scheme is not None:
+        raise ValueError("entropy-coded index streams cannot be cut at a row boundary (ranks are global); "
+                         "re-pack the shard's indices instead.")
     begin, end = shard_rows(layer.out_features, world_size, rank)
     groups = layer.in_features // layer.vector_len
     res = None

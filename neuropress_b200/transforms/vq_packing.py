@@ -89,3 +89,13 @@ class IndexPacking:
         for k in range(1, (bits + 7 + 7) // 8):
             window = window | (p[byte0 + k] << (8 * k))
         return (window >> (pos & 7)) & ((1 << bits) - 1)
+
+
+# The entropy-coded packers live in a module of their own; the reference exports them from this
+# one (``neuropress.transforms.vq_packing``), so they are importable from here too.
+from .entropy_packing import (  # noqa: E402
+    NTieredIndexPacking,
+    TieredIndexPacking,
+    ZeroEscapePacking,
+    describe_entropy_buffer,
+)

@@ -22,6 +22,7 @@ Reference locations restated here (paths inside the reference project):
                                 neuropress/kernels/q4_linear.cu:80-131
   * embedding lookups           neuropress/nn/np_vq_embedding.py:119-141
                                 neuropress/nn/np_embedding.py:120-183, 449-503
+  * entropy-coded index streams neuropress/transforms/vq_packing.py:298-1384
 """
 
 from __future__ import annotations
@@ -98,6 +99,107 @@ def unpack_indices(packed: np.ndarray, bits: int, n_indices: int) -> np.ndarray:
 # --------------------------------------------------------------------------------------
 # VQ decode and forward
 # --------------------------------------------------------------------------------------
+
+
+# --------------------------------------------------------------------------------------
+# Entropy-coded index streams (two-tier, N-tier, zero escape)
+# --------------------------------------------------------------------------------------
+
+
+def _stream_bits(buf: np.ndarray) -> np.ndarray:
+    return np.unpackbits(np.ascontiguousarray(buf, dtype=np.uint8), bitorder="little")
+
+
+def _payloads(bits: np.ndarray, first_bit: int, width: int, count: int) -> np.ndarray:
+    """``count`` consecutive ``width``-bit values (LSB first) starting at stream bit ``first_bit``."""
+    if count == 0 or width == 0:
+        return np.zeros(count, dtype=np.int64)
+    chunk = bits[first_bit:first_bit + count * width].reshape(count, width).astype(np.int64)
+    return (chunk << np.arange(width, dtype=np.int64)).sum(axis=1)
+
+
+def _u32(buf: np.ndarray, word: int) -> int:
+    return int(np.frombuffer(np.ascontiguousarray(buf[4 * word:4 * word + 4]).tobytes(), dtype="<u4")[0])
+
+
+def entropy_unpack(packed, scheme: str) -> np.ndarray:
+    """Indices of an entropy-coded buffer, decoded sequentially the way the formats are defined:
+    the prefix stream gives every index its tier, and tier t's payloads are consumed in index
+    order from tier t's stream.  ``scheme``: ``"tiered"`` (reference :298-520: header n, n_hot,
+    cold_bits[, hot_bits]; prefix bit 0 = hot), ``"ntier"`` (:612-908: magic 0x4E565154, cascaded
+    prefixes, tier k stores index - 2**bits[k-1]) or ``"zero_escape"`` (:1037-1276: magic
+    0x5A455343, two-bit prefix, payload widths 0/4/8/cold_bits, offsets 0/1/17/257).
+    Four-bit streams are padded to whole bytes (an even count), every stream starts on a byte."""
+    buf = _as_np_u8(packed)
+    bits = _stream_bits(buf)
+
+    def nbytes(count: int, width: int) -> int:
+        return (count * width + 7) // 8
+
+    if scheme == "tiered":
+        n, n_hot, cold_bits = _u32(buf, 0), _u32(buf, 1), _u32(buf, 2)
+        hot_bits, off = 4, 12
+        if buf.size >= 16 and 4 <= _u32(buf, 3) <= 16:
+            hot_bits, off = _u32(buf, 3), 16
+        tier = bits[8 * off:8 * off + n].astype(np.int64)
+        off += nbytes(n, 1)
+        widths, lows, counts = [hot_bits, cold_bits], [0, 0], [n_hot, n - n_hot]
+    elif scheme == "ntier":
+        assert _u32(buf, 0) == 0x4E565154, "not an n-tier buffer"
+        n, d = _u32(buf, 1), _u32(buf, 2)
+        counts = [_u32(buf, 3 + 2 * k) for k in range(d)]
+        widths = [_u32(buf, 4 + 2 * k) for k in range(d)]
+        lows = [0] + [1 << w for w in widths[:-1]]
+        off = 12 + 8 * d
+        tier = np.full(n, d - 1, dtype=np.int64)
+        alive = np.arange(n)
+        for k in range(d - 1):
+            later = bits[8 * off:8 * off + alive.size].astype(bool)
+            tier[alive[~later]] = k
+            off += nbytes(alive.size, 1)
+            alive = alive[later]
+    elif scheme == "zero_escape":
+        assert _u32(buf, 0) == 0x5A455343, "not a zero-escape buffer"
+        n, cold_bits = _u32(buf, 1), _u32(buf, 2)
+        counts = [_u32(buf, 3), _u32(buf, 4), _u32(buf, 5)]
+        counts.append(n - sum(counts))
+        widths, lows = [0, 4, 8, cold_bits], [0, 1, 17, 257]
+        off = 24
+        pre = bits[8 * off:8 * off + 2 * n].reshape(n, 2).astype(np.int64)
+        tier = pre[:, 0] + 2 * pre[:, 1]
+        off += nbytes(n, 2)
+    else:
+        raise ValueError(scheme)
+    out = np.zeros(n, dtype=np.int64)
+    for k, (width, low, count) in enumerate(zip(widths, lows, counts)):
+        where = np.flatnonzero(tier == k)
+        assert where.size == count, "tier counts in the header do not match the prefix stream"
+        out[where] = _payloads(bits, 8 * off, width, count) + low
+        off += nbytes(count, width)
+    return out
+
+
+def entropy_row_offsets(packed, scheme: str, n_rows: int, n_groups: int) -> list[np.ndarray]:
+    """Per tier, the number of its indices in the rows before row i (int32 ``[n_rows + 1]``): the
+    ``compute_row_offsets`` of the three packers (:522-572, :910-973, :1278-1326), restated from
+    the decoded indices."""
+    idx = entropy_unpack(packed, scheme).reshape(n_rows, n_groups)
+    buf = _as_np_u8(packed)
+    if scheme == "tiered":
+        hot_bits = _u32(buf, 3) if buf.size >= 16 and 4 <= _u32(buf, 3) <= 16 else 4
+        bounds = [1 << hot_bits]
+    elif scheme == "ntier":
+        d = _u32(buf, 2)
+        bounds = [1 << _u32(buf, 4 + 2 * k) for k in range(d - 1)]
+    else:
+        bounds = [1, 17, 257]
+    tier = np.searchsorted(np.asarray(bounds), idx, side="right")
+    out = []
+    for k in range(len(bounds) + 1):
+        off = np.zeros(n_rows + 1, dtype=np.int64)
+        off[1:] = np.cumsum((tier == k).sum(axis=1))
+        out.append(off.astype(np.int32))
+    return out
 
 
 def _as_np_u8(t) -> np.ndarray:
