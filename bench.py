@@ -693,7 +693,7 @@ def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms
         dms = sum(d[4] for d in dec)
         gbs = nbytes / (dms * 1e-3) / 1e9
         out["decode_roofline"] = {
-            "bound": "hbm", "kernel": "vq_decode_kernel (one-pass decode, bf16 out), all launches of a pass",
+            "bound": "hbm", "kernel": "vq_decode_copy_kernel (one-pass gather-copy decode, bf16 out), all launches of a pass",
             "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": f"{peak_src} copy bandwidth",
             "algorithmic_bytes": nbytes, "launch_ms_sum": round(dms, 4), "launches_per_pass": len(dec),

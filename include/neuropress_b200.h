@@ -186,6 +186,13 @@ int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_
  * Replaces the same reference code as npb_vq_gemm_fused. */
 int npb_vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int out_dtype,
                          npb_stream_t stream);
+/* The one-pass decode of a plain weight as a gather-copy from the same table: asynchronous 16-byte
+ * copies into a shared-memory chunk, written out by bulk copies; the decoded matrix is bit for bit
+ * npb_vq_decode's.  out_dtype NPB_F16 / NPB_BF16 (= the table's type), vector_len 8, bits 8 / 12 /
+ * 16, K % 64 == 0; NPB_ERR_UNSUPPORTED otherwise (call npb_vq_decode).  Replaces vq_dequant
+ * (neuropress/kernels/vq_dequant.cu:105-146) like npb_vq_decode. */
+int npb_vq_decode_cb(const npb_vq_weight* w, const void* codebook_x, int64_t N, int64_t K, void* out,
+                     int out_dtype, npb_stream_t stream);
 int npb_vq_gemm_fused_cb(const npb_vq_weight* w, const void* codebook_x, const void* x, int x_dtype,
                          int64_t M, int64_t N, int64_t K, const float* bias, void* y,
                          npb_stream_t stream);

@@ -24,6 +24,7 @@ int q_gemv(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, con
 int gemm(const void*, const void*, const float*, void*, int64_t, int64_t, int64_t, int,
          cudaStream_t);
 int vq_codebook_cast(const void*, int64_t, void*, int, cudaStream_t);
+int vq_decode_copy(const npb_vq_weight*, const void*, int64_t, int64_t, void*, int, cudaStream_t);
 int vq_entropy_expand(const npb_vq_entropy_stream*, int64_t, int64_t, void*, cudaStream_t);
 int vq_gemm_fused(const npb_vq_weight*, const void*, const void*, int, int64_t, int64_t, int64_t,
                   const float*, void*, cudaStream_t);
@@ -228,6 +229,11 @@ int npb_vq_gemm_fused(const npb_vq_weight* w, const void* x, int x_dtype, int64_
 int npb_vq_entropy_expand(const npb_vq_entropy_stream* s, int64_t N, int64_t G, void* out_u16,
                           npb_stream_t stream) {
   return npb::vq_entropy_expand(s, N, G, out_u16, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_decode_cb(const npb_vq_weight* w, const void* codebook_x, int64_t N, int64_t K, void* out,
+                     int out_dtype, npb_stream_t stream) {
+  return npb::vq_decode_copy(w, codebook_x, N, K, out, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 int npb_vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int out_dtype, npb_stream_t stream) {

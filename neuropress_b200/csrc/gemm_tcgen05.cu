@@ -809,6 +809,7 @@ int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, i
 // Reads and clears the device-side give-up record of the GEMM kernels (synchronises).
 int vq_gemm_fused_device_status(int* host_out);  // vq_gemm_fused.cu keeps its own record
 int q_gemv_ring_device_status(int* host_out);    // and so does q_gemv_ring.cu
+int vq_decode_copy_device_status(int* host_out); // and vq_decode_copy.cu
 
 int gemm_device_status(int* host_out) {
   int v = 0;
@@ -823,6 +824,9 @@ int gemm_device_status(int* host_out) {
   int vr = 0;
   if (int rc = q_gemv_ring_device_status(&vr)) return rc;
   if (v == 0 && vr != 0) v = 20 + vr;
+  int vc = 0;
+  if (int rc = vq_decode_copy_device_status(&vc)) return rc;
+  if (v == 0 && vc != 0) v = 30 + vc;
   if (host_out) *host_out = v;
   return v == 0 ? NPB_OK : NPB_ERR_DEVICE_TIMEOUT;
 }

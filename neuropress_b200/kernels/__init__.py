@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import os
 
 import torch
 
@@ -117,6 +118,17 @@ def vq_dequant(packed_indices: torch.Tensor, centroids: torch.Tensor, bits: int,
     elif out.shape != (out_features, in_features) or out.dtype != dtype or not out.is_contiguous():
         raise RuntimeError("vq_dequant: `out` has the wrong shape, dtype or layout.")
     with torch.cuda.device(packed_indices.device):
+        if (VQ_COPY_FORM and dtype in (torch.float16, torch.bfloat16) and bits in (8, 12, 16)
+                and centroids.shape[-1] == 8 and in_features % 64 == 0 and "residual_indices" not in ext
+                and "row_scale" not in ext and centroids.dtype == torch.float16 and centroids.is_contiguous()):
+            # plain weight: gather-copy from the codebook in the output type
+            table = codebook_in_dtype(centroids, dtype)
+            rc = _launch("npb_vq_decode", lib.npb_vq_decode_cb, w, table.data_ptr(), out_features, in_features,
+                         out.data_ptr(), _cabi.dtype_code(dtype), _cabi.stream_ptr())
+            if rc == 0:
+                return out
+            if rc not in (2, 4):   # unsupported size / alignment: the converting decode takes it
+                _cabi.check(rc, "vq_dequant")
         rc = _launch("npb_vq_decode", lib.npb_vq_decode, w, out_features, in_features, out.data_ptr(),
                                _cabi.dtype_code(dtype), _cabi.stream_ptr())
     _cabi.check(rc, "vq_dequant")
@@ -216,7 +228,7 @@ def vq_gemm_fused(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torc
 
 # Plain weights take the copy form of the tile-decode GEMM (``npb_vq_gemm_fused_cb``): the codebook
 # is cast once to the activation type and the kernel copies entries instead of converting them.
-VQ_COPY_FORM = True
+VQ_COPY_FORM = os.environ.get("NEUROPRESS_B200_VQ_COPY_FORM", "1") != "0"
 _cast_codebooks: dict = {}   # id(centroids) -> (weakref to it, its version, {dtype: cast tensor})
 
 

@@ -308,6 +308,39 @@ def test_vq_gemm_fused_copy_form_equals_converting_form(case, dtype, rows, monke
         assert_output_close(y_copy, _vq_forward_ref64(layer, x.cpu()), dtype, tol=2e-3)
 
 
+DECODE_COPY_CASES = [  # N, K, NC, bits, cols_per_codebook
+    (37, 64, 256, 8, 0),          # one ragged chunk (296 vectors)
+    (300, 1024, 4096, 12, 0),     # 12-bit stream, 18.75 chunks
+    (2048, 2048, 4096, 16, 512),  # one codebook per 512 columns, indices clamped + offset
+    (9000, 4096, 65536, 16, 0),   # 2250 chunks over 148 CTAs: every stage wraps many times
+    (1000, 8192, 65536, 16, 0),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_COPY_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_vq_decode_copy_form_equals_converting_form(case, dtype, monkeypatch):
+    """Plain weights decode as a pipelined gather-copy from the codebook in the output type
+    (npb_vq_decode_cb); the matrix must be the thread-per-vector decode's, bit for bit."""
+    from neuropress_b200 import _cabi
+    N, K, NC, bits, cpc = case
+    layer = make_vq_layer(N, K, num_centroids=NC, bits=bits, seed=N + bits, cols_per_codebook=cpc)
+    args = (layer.packed.to(DEV), layer.centroids.to(DEV), bits, N, K, dtype)
+    ext = _vq_ext_gpu(layer)
+    seen = []
+    monkeypatch.setattr(kernels, "_launch", lambda sym, fn, *a: (seen.append(fn.__name__), fn(*a))[1])
+    monkeypatch.setattr(kernels, "VQ_COPY_FORM", True)
+    w_copy = kernels.vq_dequant(*args, **ext)
+    assert seen[-1] == "npb_vq_decode_cb" and _cabi.gemm_device_status() == 0
+    monkeypatch.setattr(kernels, "VQ_COPY_FORM", False)
+    w_conv = kernels.vq_dequant(*args, **ext)
+    assert seen[-1] == "npb_vq_decode"
+    assert torch.equal(w_copy, w_conv)
+    if N <= 2048:
+        ref = oracle.vq_decode(layer.packed, layer.centroids, bits, N, K, dtype, **layer.ext())
+        assert torch.equal(w_copy.cpu(), ref)
+
+
 def test_vq_codebook_cast_matches_torch():
     c = (torch.randn(4096, 8, generator=torch.Generator().manual_seed(3)) * 0.02).half().to(DEV)
     assert torch.equal(kernels.codebook_in_dtype(c, torch.bfloat16), c.to(torch.bfloat16))
