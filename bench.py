@@ -636,8 +636,8 @@ def run_ours(args) -> dict:
 
 # DRAM bytes (read + write) of single launches on the unsharded gate projection at 4096 rows, from one
 # `ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum` capture of `--case c5:gate:4096`.
-NCU_GATE_GEMM_DRAM_BYTES = 1401767168 + 224070144
-NCU_GATE_DECODE_DRAM_BYTES = 59784704 + 413511680
+NCU_GATE_GEMM_DRAM_BYTES = 1747335680 + 224843008
+NCU_GATE_DECODE_DRAM_BYTES = 59789568 + 411090176
 
 
 def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms_per_pass: float) -> dict:
@@ -698,7 +698,7 @@ def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms
             "frac": round(gbs / peaks["hbm_gbs"], 4), "peak_source": f"{peak_src} copy bandwidth",
             "algorithmic_bytes": nbytes, "launch_ms_sum": round(dms, 4), "launches_per_pass": len(dec),
             "share_of_pass": round(dms / total, 3),
-            # measured on the gate decode (59.8 MB read + 413.5 MB written of 58.7 + 1.0 + 469.8 MB
+            # measured on the gate decode (59.8 MB read + 411.1 MB written of 58.7 + 1.0 + 469.8 MB
             # algorithmic: the tail of the output is still dirty in L2 when the kernel ends), applied
             # to the pass by the same ratio
             "traffic": int(nbytes * NCU_GATE_DECODE_DRAM_BYTES / (28672 * 1024 * 2 + 28672 * 8192 * 2)),
