@@ -611,6 +611,7 @@ def run_ours(args) -> dict:
         for key, fn in (("c2", lambda: run_c2(device, peaks, peak_src)),
                         ("c3", lambda: run_c3(device, peaks, peak_src)),
                         ("practical_roofs", lambda: run_probes(device, peaks)),
+                        ("entropy_streams", lambda: run_entropy(device, peaks)),
                         ("c4", lambda: run_c4(device, peaks))):
             try:
                 line[key] = fn()
@@ -712,6 +713,62 @@ def c5_rooflines(kmean: dict, world: int, wl: C5, peaks: dict, peak_src: str, ms
     out["hbm_floor_decode_batch_ms"] = round(wl.local_index_bytes / peaks["hbm_gbs"] / 1e6, 4)
     out["tensor_floor_prefill_ms"] = round(
         sum(2.0 * 4096 * local_n(name, n) * k for name, n, k in C5_LINEARS) / peaks["bf16_tflops_sustained"] / 1e9, 4)
+    return out
+
+
+# --------------------------------------------------------------------------- entropy extra ---
+def run_entropy(device, peaks: dict) -> dict:
+    """Entropy-coded index streams on the c2-shaped layer (14336 x 4096, 65536-entry codebook,
+    Zipf(1.1)-distributed indices): coded size, the expansion kernel alone (CUDA events over
+    back-to-back launches; algorithmic bytes = coded bytes in + 2 bytes per index out) and the
+    1-row forward of the coded layer (expansion + GEMV) beside the plain layer's."""
+    from neuropress_b200 import kernels
+    from neuropress_b200.nn import NPVQLinear, VQProxy
+    from neuropress_b200.transforms.vq_packing import (IndexPacking, NTieredIndexPacking, TieredIndexPacking,
+                                                       ZeroEscapePacking, describe_entropy_buffer)
+
+    n, k, nc = N_OUT, K_IN, 65536
+    g = k // 8
+    gen = torch.Generator(device=device).manual_seed(77)
+    w = 1.0 / torch.arange(1, nc + 1, dtype=torch.float32, device=device) ** 1.1
+    idx = torch.multinomial(w / w.sum(), n * g, replacement=True, generator=gen)
+    proxy = VQProxy(device_normal((nc, 8), device, 78, std=0.02, dtype=torch.float16))
+    x = device_normal((1, k), device, 79)
+
+    def timed(fn, reps=30):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / reps * 1e3
+
+    plain = NPVQLinear(proxy, IndexPacking.pack(idx, 16), 16, n, k, 8, "cuda_wmma")
+    out = {"workload": f"{n} x {k}, {nc}-entry codebook, Zipf(1.1) indices", "plain_bytes": n * g * 2,
+           "plain_forward_1row_us": round(timed(lambda: plain(x)), 2), "schemes": {}}
+    schemes = (("tiered_hot8", "tiered", lambda: TieredIndexPacking.pack(idx, 16, 8), dict(use_tiered=True, cold_bits=16)),
+               ("ntier_4_8_12_16", "ntier", lambda: NTieredIndexPacking.pack(idx, [4, 8, 12, 16]), dict(tier_bits=[4, 8, 12, 16])),
+               ("zero_escape", "zero_escape", lambda: ZeroEscapePacking.pack(idx, 16), dict(zero_escape=True)))
+    for tag, scheme, pack, kw in schemes:
+        buf = pack()
+        layer = NPVQLinear(proxy, buf, 16, n, k, 8, "auto", **kw)
+        lay = describe_entropy_buffer(buf, scheme)
+        offs = [getattr(layer, nm) for nm in layer._entropy_names]
+        table = torch.empty(n * g * 2, dtype=torch.uint8, device=device)
+        us = timed(lambda: kernels.vq_entropy_expand(buf, lay, offs, n, g, out=table))
+        assert torch.equal(table.view(torch.int16).to(torch.int64) & 0xFFFF, idx), tag
+        out["schemes"][tag] = {
+            "coded_bytes": buf.numel(), "bits_per_index": round(buf.numel() * 8 / (n * g), 3),
+            "expand_us": round(us, 2),
+            "expand_GBps": round((buf.numel() + n * g * 2) / (us * 1e-6) / 1e9, 1),
+            "frac_of_hbm": round((buf.numel() + n * g * 2) / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 4),
+            "forward_1row_us": round(timed(lambda: layer(x)), 2),
+        }
+        del layer, buf, table
     return out
 
 
