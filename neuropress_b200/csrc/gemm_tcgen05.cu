@@ -22,6 +22,7 @@
 // Stands in for: cuBLAS via F.linear (neuropress/nn/np_vq_linear.py:1148) and, for group-affine
 // weights, the per-row GEMV the reference runs at every batch size
 // (neuropress/kernels/q4_linear.cu:80-131).
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -734,6 +735,15 @@ int gemm_fused_mt(const void* x, GemmParams p, cudaStream_t st) {
   }
 }
 
+// NEUROPRESS_B200_Q_GEMM_STAGED=0 keeps npb_q_gemm_fused on the register-fetching form.
+bool q_staged_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("NEUROPRESS_B200_Q_GEMM_STAGED");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int check_gemm_common(const void* x, const void* y, int64_t M, int64_t N, int64_t K, int dtype) {
   if (M < 0 || N < 0 || K < 0) return NPB_ERR_INVALID_ARG;
   if (dtype != NPB_BF16 && dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
@@ -786,6 +796,11 @@ int gemm_gather(const void* x, const void* w, const float* bias, int64_t M, int6
   return gemm_impl(x, w, bias, nullptr, M, N, K, dtype, &sink, st);
 }
 
+// q_gemm_staged.cu: the form whose raw codes / scales arrive by TMA (NPB_ERR_UNSUPPORTED outside its domain)
+int q_gemm_staged(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
+                  const float* bias, void* y, cudaStream_t st);
+int q_gemm_staged_device_status(int* host_out);
+
 int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
                  const float* bias, void* y, cudaStream_t st) {
   if (int rc = validate_q(w, N, K)) return rc;
@@ -793,6 +808,10 @@ int q_gemm_fused(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, i
   if (M == 0 || N == 0) return NPB_OK;
   if (w->nbits != 4 || K % 64 != 0 || w->group_size % 32 != 0) return NPB_ERR_UNSUPPORTED;
   if (!aligned_to(w->codes, 16)) return NPB_ERR_ALIGNMENT;
+  if (q_staged_enabled()) {
+    const int rc = q_gemm_staged(w, x, x_dtype, M, N, K, bias, y, st);
+    if (rc != NPB_ERR_UNSUPPORTED) return rc;
+  }
   GemmParams p{};
   p.bias = bias;
   p.y = y;
@@ -827,6 +846,9 @@ int gemm_device_status(int* host_out) {
   int vc = 0;
   if (int rc = vq_decode_copy_device_status(&vc)) return rc;
   if (v == 0 && vc != 0) v = 30 + vc;
+  int vs = 0;
+  if (int rc = q_gemm_staged_device_status(&vs)) return rc;
+  if (v == 0 && vs != 0) v = 40 + vs;
   if (host_out) *host_out = v;
   return v == 0 ? NPB_OK : NPB_ERR_DEVICE_TIMEOUT;
 }

@@ -458,12 +458,13 @@ def q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point=None, bias=None
 
 
 # Whether q_linear's mid band (9..Q_FUSED_MAX_ROWS rows) runs the tile-dequant GEMM
-# (``npb_q_gemm_fused``); when False it decodes once and runs the dense GEMM.  Off: with the
-# packed-fp32 decode kernel the pair is as fast or faster on every shape measured on a B200
-# (14336 x 4096: 50 / 56 / 74 us at 128 / 256 / 384 rows against 51 / 59 / 82 us fused;
-# 4096 x 4096: 32 us against 50 us, the fused kernel having only 32 CTAs there).
-Q_TILE_DEQUANT_GEMM = False
+# (``npb_q_gemm_fused``) instead of decoding once and running the dense GEMM.  On: with the raw
+# codes / scales staged by TMA (csrc/q_gemm_staged.cu) it is the faster of the two on a B200
+# (14336 x 4096, Q4_0: 37 / 38 / 46 / 57 us at 16 / 128 / 256 / 384 rows against 49 / 50 / 56 / 75 us).
+# NEUROPRESS_B200_Q_TILE_DEQUANT=0 switches it off.
+Q_TILE_DEQUANT_GEMM = os.environ.get("NEUROPRESS_B200_Q_TILE_DEQUANT", "1") != "0"
 Q_FUSED_MAX_ROWS = 384
+Q_FUSED_MIN_WEIGHTS = 1 << 25   # smaller layers (4096 x 4096: 34 us against 31 us at 256 rows) decode + GEMM
 
 
 def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: int,
@@ -471,8 +472,8 @@ def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: 
              bias: torch.Tensor | None = None, gather=None) -> torch.Tensor:
     """Drop-in for the reference's ``q_linear`` (kernels/__init__.py:109-151): ``x`` is
     ``[..., K]``, output ``[..., N]`` in ``x.dtype``.  The reference runs one GEMV kernel for
-    every row count (q4_linear.cu:137-140); here rows are banded: GEMV up to 8 rows, then
-    decode once + dense GEMM (or, opt-in, the tile-dequant GEMM for the mid band).  ``gather``
+    every row count (q4_linear.cu:137-140); here rows are banded: GEMV up to 8 rows, the
+    tile-dequant GEMM up to 384 rows, then decode once + dense GEMM.  ``gather``
     (a ``sharding.PushGather``; not in the reference): the weight is an out-feature shard and the
     all-gathered ``[..., N_full]`` is returned -- by the GEMM's own epilogue where it can."""
     k = w_pack.shape[1] * (8 // nbits)
@@ -489,7 +490,7 @@ def q_linear(x: torch.Tensor, w_pack: torch.Tensor, scale: torch.Tensor, nbits: 
     if x.dtype not in (torch.float16, torch.bfloat16):
         raise RuntimeError("q_linear: more than 8 rows need fp16 or bf16 activations.")
     if (Q_TILE_DEQUANT_GEMM and m <= Q_FUSED_MAX_ROWS and nbits == 4 and k % 64 == 0
-            and group_size % 32 == 0):
+            and group_size % 32 == 0 and w_pack.shape[0] * k >= Q_FUSED_MIN_WEIGHTS):
         return pushed(q_gemm_fused(x, w_pack, scale, nbits, group_size, zero_point, bias))
     w = q_dequant(w_pack, scale, nbits, group_size, zero_point, x.dtype)
     if gather is not None and gather.accepts(m, x.dtype):
