@@ -254,6 +254,8 @@ FUSED_CASES = [
     (256, 512, 4096, 16, 0, False, 0),
     (200, 1024, 4096, 12, 0, False, 0),
     (384, 512, 65536, 16, 256, True, 0),
+    (1000, 2048, 4096, 12, 16, False, 0),   # residual only, 12-bit, N tail
+    (264, 1024, 4096, 16, 0, True, 512),    # row scale only, one codebook per 512 columns
     (128, 2048, 4096, 16, 0, False, 512),
     (130, 256, 256, 8, 0, False, 0),
     (72, 128, 1024, 10, 0, False, 0),
