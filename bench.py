@@ -488,9 +488,18 @@ def run_ours(args) -> dict:
 
     # ---- end to end: pinned host inputs -> device -> forwards -> pinned host outputs ----
     h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
-    xs_host = {rows: {k: v.cpu().pin_memory() for k, v in wl.x[rows].items()} for rows in C5_ROWS}
+    # N > 1: a rank uploads only its 1/N of every activation matrix's rows (all PCIe links work in
+    # parallel) and the ranks all-gather the slices over NVLink (NCCL), so the replicated inputs cross
+    # PCIe once in total, not once per rank.
+    def row_slice(rows: int) -> slice:
+        per = rows // world
+        return slice(rank * per, (rank + 1) * per)
+
+    xs_host = {rows: {k: v[row_slice(rows)].cpu().pin_memory() for k, v in wl.x[rows].items()} for rows in C5_ROWS}
     stage = [{rows: {k: torch.empty_like(v) for k, v in wl.x[rows].items()} for rows in C5_ROWS}
              for _ in range(2)]
+    part = [{rows: {k: torch.empty_like(v[row_slice(rows)]) for k, v in wl.x[rows].items()} for rows in C5_ROWS}
+            for _ in range(2)] if world > 1 else None
     ys_host = {}
     d2h_bytes = 0
     for rows in C5_ROWS:
@@ -500,7 +509,7 @@ def run_ours(args) -> dict:
                 continue                       # replicated linears: rank 0 returns the result
             ys_host[(name, rows)] = torch.empty((rows, e - b), dtype=torch.bfloat16).pin_memory()
             d2h_bytes += rows * (e - b) * 2
-    h2d_bytes = sum(v.numel() * 2 for rows in C5_ROWS for v in wl.x[rows].values())
+    h2d_bytes = sum(v.numel() * 2 for rows in C5_ROWS for v in xs_host[rows].values())
     ev_free = [torch.cuda.Event() for _ in range(2)]
     for ev in ev_free:
         ev.record()
@@ -512,7 +521,12 @@ def run_ours(args) -> dict:
             h2d.wait_event(ev_free[q & 1])     # the pass that last used this staging set is done
             for rows in C5_ROWS:
                 for k, v in st[rows].items():
-                    v.copy_(xs_host[rows][k], non_blocking=True)
+                    if world == 1:
+                        v.copy_(xs_host[rows][k], non_blocking=True)
+                    else:
+                        mine = part[q & 1][rows][k]
+                        mine.copy_(xs_host[rows][k], non_blocking=True)
+                        dist.all_gather_into_tensor(v, mine)
             ready = torch.cuda.Event()
             ready.record(h2d)
         cur.wait_event(ready)
@@ -594,8 +608,9 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": h2d_bytes * PASSES_PER_STEP,
                 "d2h_bytes_per_step": d2h_bytes * PASSES_PER_STEP,
                 "ms_per_step": round(e2e_ms / steps, 4),
-                "note": "per rank; every rank uploads the replicated activations and returns its own "
-                        "output columns" if world > 1 else "all inputs up, all outputs down"},
+                "note": "per rank: uploads 1/N of the rows of every activation matrix (the ranks all-gather them "
+                        "over NVLink with NCCL) and returns its own output columns" if world > 1
+                        else "all inputs up, all outputs down"},
         "gpu_launches": launches_per_pass * PASSES_PER_STEP * steps,
         "clocks": clocks.summary(), "clocks_e2e": clocks_e2e.summary(),
         "parity": parity,
@@ -1195,7 +1210,7 @@ def run_case(args) -> dict:
       q40:ROWS / hqq:ROWS       group-affine 14336 x 4096
       c5:NAME:ROWS one linear of the headline layer set (NAME in q k v o gate up down)
       c5pass       the headline layer set, eager passes (the launch list)
-      probes       the hardware-rate probes; c4 the decoder stack"""
+      probes       the hardware-rate probes; c4 the decoder stack; entropy the entropy-coded streams"""
     from neuropress_b200 import kernels
 
     torch.cuda.set_device(0)
@@ -1222,6 +1237,8 @@ def run_case(args) -> dict:
         return run_probes(device, peaks)
     if name == "c4":
         return run_c4(device, peaks)
+    if name == "entropy":
+        return run_entropy(device, peaks)
     if name == "c2":
         return run_c2(device, peaks, peak_src)
     if name == "c3":

@@ -134,6 +134,9 @@ entropy_expand_kernel(const EntropyDev e, int64_t N, int G, uint16_t* __restrict
     for (int k = 0; k < D; ++k)
       rank_base[k] = tier_rank0[k] + tier_seen[k] + warp_excl_scan(cnt[k], lane, tot[k]);
 
+    // whole groups of eight indices at 16-byte aligned places take vector stores
+    const bool vec_ok = (valid & 7) == 0 && ((reinterpret_cast<uintptr_t>(dst_row + first) & 15u) == 0);
+    uint32_t acc[4] = {0, 0, 0, 0};
     for (int j = 0; j < valid; ++j) {
       int k = 0, r = 0;
       if (KIND == 1) {
@@ -157,7 +160,15 @@ entropy_expand_kernel(const EntropyDev e, int64_t N, int G, uint16_t* __restrict
       uint32_t v = (uint32_t)e.tier_lo[k];
       const int nb = e.tier_bits[k];
       if (nb > 0) v += read_bits32(e, e.tier_bit[k] + (pick4(rank_base, k) + r) * nb) & low_mask(nb);
-      dst_row[first + j] = (uint16_t)min(v, 65535u);
+      v = min(v, 65535u);
+      if (vec_ok) {
+        // eight indices per 16-byte store (a lane's run of 2-byte stores would touch a sector each)
+        const int q = j & 7;
+        if (q & 1) acc[q >> 1] |= v << 16; else acc[q >> 1] = v;
+        if (q == 7) *reinterpret_cast<uint4*>(dst_row + first + j - 7) = make_uint4(acc[0], acc[1], acc[2], acc[3]);
+      } else {
+        dst_row[first + j] = (uint16_t)v;
+      }
     }
 #pragma unroll
     for (int k = 0; k < D; ++k) tier_seen[k] += tot[k];
