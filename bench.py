@@ -616,6 +616,15 @@ def run_ours(args) -> dict:
         "parity": parity,
     }
     line.update(c5_rooflines(kmean, world, wl, peaks, peak_src, total_ms / steps / PASSES_PER_STEP))
+    if world > 1:
+        # what the all-gathers move: every rank receives the other ranks' columns of every sharded output
+        recv = sum(rows * (n - n // world) * 2 for rows in C5_ROWS for name, n, _ in C5_LINEARS if wl.sharded[name])
+        line["nvlink"] = {
+            "received_bytes_per_pass_per_gpu": recv,
+            "note": "algorithmic (P-1)/P * 2*M*N of the sharded linears; the fused epilogues and the push kernel "
+                    "store every tile once per peer, so sent = received = algorithmic",
+            "GBps_per_gpu_over_the_pass": round(recv / (total_ms / steps / PASSES_PER_STEP * 1e-3) / 1e9, 1),
+        }
     if world == 1 and not args.no_extras:
         del graphs
         for a in wl.ahead:
