@@ -679,6 +679,12 @@ int launch_gemm(const void* x, const void* w_dense, GemmParams p, cudaStream_t s
 // Tile width for the dense GEMM: minimise (waves x tile cost) with a mild preference for
 // wide tiles (fewer shared-memory bytes per flop).
 int pick_bn(int64_t M, int64_t N, int cg) {
+  static const int forced = [] {
+    const char* e = getenv("NEUROPRESS_B200_GEMM_BN");
+    const int v = e ? atoi(e) : 0;
+    return (v == 256 || v == 224 || v == 192 || v == 128 || v == 64) ? v : 0;
+  }();
+  if (forced) return forced;
   const int cands[5] = {256, 224, 192, 128, 64};
   const int sms = sm_count() / cg;
   const int64_t tm = (M + BM * cg - 1) / (BM * cg);
@@ -687,7 +693,10 @@ int pick_bn(int64_t M, int64_t N, int cg) {
   for (int bn : cands) {
     const int64_t tiles = tm * ((N + bn - 1) / bn);
     const int64_t waves = (tiles + sms - 1) / sms;
-    const double eff = bn >= 192 ? 1.0 : bn == 128 ? 1.12 : 1.5;
+    // cost per column of a tile: narrower tiles move more operand bytes from L2 per flop, which is what
+    // bounds the kernel (on CTA pairs 224 columns measured 10 % slower per flop than 256)
+    double eff = bn >= 192 ? 1.0 : bn == 128 ? 1.12 : 1.5;
+    if (cg == 2) eff = bn == 256 ? 1.0 : bn == 224 ? 1.07 : bn == 192 ? 1.12 : bn == 128 ? 1.25 : 1.6;
     const double cost = (double)waves * bn * eff;
     if (cost < best - 1e-9) { best = cost; best_bn = bn; }
   }
