@@ -206,6 +206,13 @@ int npb_vq_gemm_fused_cb(const npb_vq_weight* w, const void* codebook_x, const v
 int npb_vq_entropy_expand(const npb_vq_entropy_stream* s, int64_t N, int64_t G, void* out_u16,
                           npb_stream_t stream);
 
+/* LUT gather: out[m, n] = sum over g of lut[m, g, idx[n, g]], lut fp32 [M, G, NC] built by the
+ * caller (one matmul of the activations with the codebook), idx the packed index stream of N * G
+ * indices of `bits` bits, out fp32 [M, N].  Replaces vq_lut_gather
+ * (neuropress/kernels/vq_linear_lut.cu:121-206, pybind :208-211).  M <= 65535. */
+int npb_vq_lut_gather(const float* lut, int64_t M, int64_t G, int64_t NC, const uint8_t* packed,
+                      int64_t packed_bytes, int bits, int64_t N, float* out, npb_stream_t stream);
+
 /* Same for group-affine weights (no reference counterpart beyond q_linear, which re-reads
  * the weight per row: neuropress/kernels/q4_linear.cu:80-131). nbits 4, K % 64 == 0,
  * group_size % 32 == 0 (NPB_ERR_UNSUPPORTED otherwise: decode, then npb_gemm). */

@@ -36,7 +36,7 @@ SOURCES = [
     "gemm_tcgen05.cu",
     "vq_gemm_fused.cu",
     "static_scratch.cu",
-    "allgather_push.cu", "rms_norm.cu", "vq_gemv_mma.cu", "embedding.cu", "vq_entropy.cu", "vq_decode_copy.cu", "q_gemm_staged.cu",
+    "allgather_push.cu", "rms_norm.cu", "vq_gemv_mma.cu", "embedding.cu", "vq_entropy.cu", "vq_decode_copy.cu", "q_gemm_staged.cu", "vq_lut.cu",
 ]
 
 NVCC_FLAGS = [

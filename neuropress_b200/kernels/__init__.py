@@ -320,6 +320,24 @@ def vq_entropy_expand(packed: torch.Tensor, layout: dict, row_offsets: list[torc
     return out
 
 
+def vq_lut_gather(lut: torch.Tensor, packed_indices: torch.Tensor, bits: int, out_features: int) -> torch.Tensor:
+    """LUT gather phase ``y[m, j] = sum_g lut[m, g, idx[j, g]]`` (reference: ``vq_lut_gather``,
+    kernels/__init__.py:405-426, vq_linear_lut.cu:121-206).  ``lut`` is the caller's fp32
+    ``[M, n_groups, NC]`` table ``(x.reshape(M * n_groups, VL) @ centroids.T).reshape(M, n_groups, NC)``;
+    returns fp32 ``[M, out_features]``."""
+    _cabi.require_cuda("vq_lut_gather", lut, packed_indices)
+    if lut.dtype != torch.float32 or lut.dim() != 3:
+        raise RuntimeError("vq_lut_gather: lut must be a 3-D float32 tensor [M, n_groups, NC].")
+    lib = _cabi.load_library()
+    m, g, nc = lut.shape
+    out = torch.empty((m, out_features), dtype=torch.float32, device=lut.device)
+    with torch.cuda.device(lut.device):
+        rc = _launch("npb_vq_lut_gather", lib.npb_vq_lut_gather, lut.data_ptr(), m, g, nc, packed_indices.data_ptr(),
+                     packed_indices.numel(), bits, out_features, out.data_ptr(), _cabi.stream_ptr())
+    _cabi.check(rc, "vq_lut_gather")
+    return out
+
+
 def vq_dequant_gemm(x: torch.Tensor, packed_indices: torch.Tensor, centroids: torch.Tensor,
                     bits: int, out_features: int | None = None, bias: torch.Tensor | None = None,
                     **ext) -> torch.Tensor:

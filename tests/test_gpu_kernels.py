@@ -191,6 +191,29 @@ def test_q_gemv_ring_shapes(asym, gs, dtype, rows, shape):
     assert _cabi.gemm_device_status() == 0
 
 
+# ------------------------------------------------------------------------- LUT gather ---
+@pytest.mark.parametrize("bits,nc", [(4, 16), (8, 256), (10, 1000), (12, 4096), (16, 5000)])
+@pytest.mark.parametrize("shape", [(37, 96, 1), (256, 512, 3), (100, 40, 16)])
+def test_vq_lut_gather_matches_the_reference_formula(bits, nc, shape):
+    """y[m, j] = sum_g lut[m, g, idx[j, g]] with lut = x_groups @ C^T, the reference's cuda_lut
+    arithmetic (np_vq_linear.py:1189-1248, vq_linear_lut.cu:121-206); fp32, summation order free."""
+    n, k, m = shape
+    vl = 4
+    g = k // vl
+    gen = torch.Generator().manual_seed(bits + n)
+    cent = (torch.randn(nc, vl, generator=gen) * 0.05).half()
+    idx = torch.randint(0, nc, (n, g), generator=gen)
+    x = torch.randn(m, k, generator=gen)
+    lut = (x.reshape(m * g, vl) @ cent.float().T).reshape(m, g, nc).contiguous()
+    packed = torch.from_numpy(oracle.pack_indices(idx.numpy().reshape(-1), bits))
+    y = kernels.vq_lut_gather(lut.to(DEV), packed.to(DEV), bits, n)
+    assert y.dtype == torch.float32 and y.shape == (m, n)
+    ref = lut.double().gather(2, idx.T.unsqueeze(0).expand(m, g, n)).sum(1)      # [m, n]
+    assert_output_close(y, ref, torch.float32, tol=1e-5)
+    w = cent.float()[idx].reshape(n, k)                                            # the same product, decoded
+    assert_output_close(y, x.double() @ w.double().T, torch.float32, tol=1e-4)
+
+
 # ------------------------------------------------------------------- dense tcgen05 GEMM ---
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 512), (256, 512, 1024),
                                    (130, 72, 96), (1, 64, 64), (2048, 1024, 512), (300, 14336, 256)])
