@@ -1129,6 +1129,16 @@ def run_c4(device, peaks, layers_n: int = 16, bits: int = 16) -> dict:
                                        "TFLOPs_linears": round(2.0 * 512 * (index_bytes // 2 * 8) / (ms * 1e-3) / 1e12, 1)}
 
     measure("_one_launch_per_module")
+    # the 112 linears alone (same modules, one launch each, CUDA-graph replay): their share of a step; the
+    # rest is attention / RoPE / norms / residual adds in torch
+    lins = [m for m in model.modules() if isinstance(m, NPVQLinear)]
+    with torch.no_grad():
+        for batch in (1, 8, 64):
+            xs = {k: device_normal((batch, k), device, 70 + k % 97) for k in {m.in_features for m in lins}}
+            ms = graph_time_ms([(lambda m=m, x=xs[m.in_features]: m(x)) for m in lins], reps=3) * len(lins)
+            key = f"decode_batch{batch}_one_launch_per_module"
+            out[key]["linears_alone_ms"] = round(ms, 4)
+            out[key]["linears_share_of_step"] = round(ms / out[key]["ms_per_step"], 3)
     # q / k / v and gate / up as one launch each, the norm in front of them folded in
     from neuropress_b200.nn import group_shared_input_linears
 
@@ -1137,6 +1147,8 @@ def run_c4(device, peaks, layers_n: int = 16, bits: int = 16) -> dict:
     b1 = out.get("decode_batch1")
     if b1:
         out["frac_of_hbm_ceiling_batch1"] = round(b1["tokens_per_s"] / out["hbm_ceiling_tok_s_batch1"], 4)
+        out["frac_of_hbm_ceiling_batch1_linears_alone"] = round(
+            1e3 / out["decode_batch1_one_launch_per_module"]["linears_alone_ms"] / out["hbm_ceiling_tok_s_batch1"], 4)
     return out
 
 

@@ -206,6 +206,15 @@ int npb_vq_gemm_fused_cb(const npb_vq_weight* w, const void* codebook_x, const v
 int npb_vq_entropy_expand(const npb_vq_entropy_stream* s, int64_t N, int64_t G, void* out_u16,
                           npb_stream_t stream);
 
+/* npb_vq_gemm_fused_cb for up to four plain weights that share the activations (q / k / v, gate / up)
+ * in one launch: y is [M, sum of Ns], weight i's outputs in the columns after those of the weights
+ * before it; codebooks_x[i] is weight i's codebook in x_dtype; biases may be NULL or hold NULLs.  The
+ * weights must agree in bits, num_centroids and cols_per_codebook.  Same bits out as n_weights
+ * separate calls.  No reference counterpart (the reference launches each linear by itself). */
+int npb_vq_gemm_fused_grouped(const npb_vq_weight* weights, int n_weights, const void* const* codebooks_x,
+                              const int64_t* Ns, const float* const* biases, const void* x, int x_dtype,
+                              int64_t M, int64_t K, void* y, npb_stream_t stream);
+
 /* LUT gather: out[m, n] = sum over g of lut[m, g, idx[n, g]], lut fp32 [M, G, NC] built by the
  * caller (one matmul of the activations with the codebook), idx the packed index stream of N * G
  * indices of `bits` bits, out fp32 [M, N].  Replaces vq_lut_gather

@@ -39,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "npb_vq_gemm_fused_cb",
     "npb_vq_codebook_cast",
     "npb_vq_lut_gather",
+    "npb_vq_gemm_fused_grouped",
     "npb_vq_decode_cb",
     "npb_vq_entropy_expand",
     "npb_q_gemm_fused",
@@ -150,6 +151,8 @@ def load_library() -> ctypes.CDLL:
     lib.npb_vq_gemm_fused.argtypes = [vq_p, *gemv_tail]
     lib.npb_vq_gemm_fused_cb.argtypes = [vq_p, c_void_p, *gemv_tail]
     lib.npb_vq_codebook_cast.argtypes = [c_void_p, c_int64, c_void_p, c_int, c_void_p]
+    lib.npb_vq_gemm_fused_grouped.argtypes = [vq_p, c_int, POINTER(c_void_p), POINTER(c_int64), POINTER(c_void_p),
+                                              c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p]
     lib.npb_vq_lut_gather.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_int64,
                                       c_void_p, c_void_p]
     lib.npb_vq_decode_cb.argtypes = [vq_p, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p]

@@ -24,6 +24,8 @@ int q_gemv(const npb_q_weight*, const void*, int, int64_t, int64_t, int64_t, con
 int gemm(const void*, const void*, const float*, void*, int64_t, int64_t, int64_t, int,
          cudaStream_t);
 int vq_codebook_cast(const void*, int64_t, void*, int, cudaStream_t);
+int vq_gemm_fused_grouped(const npb_vq_weight*, int, const void* const*, const int64_t*, const float* const*,
+                          const void*, int, int64_t, int64_t, void*, cudaStream_t);
 int vq_lut_gather(const float*, int64_t, int64_t, int64_t, const uint8_t*, int64_t, int, int64_t, float*, cudaStream_t);
 int vq_decode_copy(const npb_vq_weight*, const void*, int64_t, int64_t, void*, int, cudaStream_t);
 int vq_entropy_expand(const npb_vq_entropy_stream*, int64_t, int64_t, void*, cudaStream_t);
@@ -240,6 +242,13 @@ int npb_vq_decode_cb(const npb_vq_weight* w, const void* codebook_x, int64_t N, 
 int npb_vq_lut_gather(const float* lut, int64_t M, int64_t G, int64_t NC, const uint8_t* packed,
                       int64_t packed_bytes, int bits, int64_t N, float* out, npb_stream_t stream) {
   return npb::vq_lut_gather(lut, M, G, NC, packed, packed_bytes, bits, N, out, static_cast<cudaStream_t>(stream));
+}
+
+int npb_vq_gemm_fused_grouped(const npb_vq_weight* weights, int n_weights, const void* const* codebooks_x,
+                              const int64_t* Ns, const float* const* biases, const void* x, int x_dtype, int64_t M,
+                              int64_t K, void* y, npb_stream_t stream) {
+  return npb::vq_gemm_fused_grouped(weights, n_weights, codebooks_x, Ns, biases, x, x_dtype, M, K, y,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 int npb_vq_codebook_cast(const void* centroids, int64_t n_values, void* out, int out_dtype, npb_stream_t stream) {

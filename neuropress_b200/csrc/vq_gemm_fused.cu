@@ -60,6 +60,19 @@ constexpr int kThreads = 192 + 32 * kDecodeWarps;   // 704
 constexpr int kBarrierBytes = 1024;
 constexpr int kResTableBytes = 256 * 16;
 
+// Grouped launch: up to four plain weights that share the activations (q / k / v, gate / up) are the
+// row segments of one tall W; a tile never straddles two segments.
+constexpr int kMaxSegs = 4;
+struct Seg {
+  const uint8_t* packed;   // the segment's index stream
+  const void* cb_x;        // its codebook in the activation type (copy form), else null
+  const __half* centroids; // its fp16 codebook
+  const float* bias;       // or null
+  int N;                   // its output features
+  int tile0;               // first N-tile of the segment
+  int col0;                // its first output column
+};
+
 struct FusedParams {
   const uint8_t* packed;
   int64_t packed_bytes;
@@ -76,7 +89,17 @@ struct FusedParams {
   int has_res, has_scale;
   int clamp;                     // copy form: indices can exceed the codebook (NC < 2^bits) or take an offset
   int M, N, K, BN, tiles_m, tiles_n, groups, warps_per_group;
+  int n_segs, ld_y;              // segments of a grouped launch (1: the plain call) and the row pitch of y
+  Seg seg[kMaxSegs];
 };
+
+__device__ __forceinline__ const Seg& seg_of(const FusedParams& p, int tn) {
+  int s = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxSegs; ++i)
+    if (i < p.n_segs && tn >= p.seg[i].tile0) s = i;
+  return p.seg[s];
+}
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
@@ -115,10 +138,11 @@ struct RawRow {
 };
 
 template <int BITS>
-__device__ __forceinline__ void fetch_row(RawRow<BITS>& it, const FusedParams& p, int n, int kb) {
+__device__ __forceinline__ void fetch_row(RawRow<BITS>& it, const FusedParams& p, const uint8_t* packed, int n,
+                                          int kb) {
   if constexpr (BITS != 0) {
     const int64_t chunk = (int64_t)n * (p.K >> 6) + kb;  // 8-index chunks per row = K / 64
-    const uint8_t* q = p.packed + chunk * BITS;
+    const uint8_t* q = packed + chunk * BITS;
     if constexpr (BITS == 16) {
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(q));
       it.w[0] = v.x; it.w[1] = v.y; it.w[2] = v.z; it.w[3] = v.w;
@@ -220,8 +244,8 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
 // Copy form of emit_row: the eight vectors of (row n, k block kb) go from the activation-type
 // codebook to their swizzle chunks as asynchronous copies.
 template <int BITS>
-__device__ __forceinline__ void emit_row_copy(const RawRow<BITS>& it, const FusedParams& p, bool valid, int kb,
-                                              uint32_t b_stage, int row) {
+__device__ __forceinline__ void emit_row_copy(const RawRow<BITS>& it, const FusedParams& p, const void* cb_x,
+                                              bool valid, int kb, uint32_t b_stage, int row) {
   // chunk c of tile row `row` lives at (row * 128) + ((c ^ (row & 7)) << 4) = base ^ (c << 4)
   const uint32_t base = b_stage + row * 128 + ((row & 7) << 4);
   uint32_t idx[8];
@@ -233,7 +257,7 @@ __device__ __forceinline__ void emit_row_copy(const RawRow<BITS>& it, const Fuse
 #pragma unroll
     for (int c = 0; c < 8; ++c) idx[c] = min(idx[c] + off, last);
   }
-  const char* cb = static_cast<const char*>(p.cb_x);
+  const char* cb = static_cast<const char*>(cb_x);
   const uint32_t nbytes = valid ? 16u : 0u;  // rows past N: zeros (their columns are never stored)
 #pragma unroll
   for (int c = 0; c < 8; ++c) cp_async_16(base ^ (uint32_t)(c << 4), cb + ((size_t)idx[c] << 4), nbytes);
@@ -360,6 +384,8 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
     int it = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const Seg& sg = seg_of(p, tn);            // the weight this tile belongs to
+      const int seg_n0 = (tn - sg.tile0) * BN;  // the tile's first output feature inside it
       const int buf = (nbuf == 2) ? (it & 1) : 0;
       const uint32_t buf_ph = (nbuf == 2) ? ((it >> 1) & 1) : (it & 1);
       const bool got = mbar_wait_bounded(&tmem_full[buf], buf_ph, abort_flag, p.wait_ns, 256u);
@@ -378,17 +404,17 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
           uint32_t v[16];
           tmem_ld_32x32_x16(acc + mt * BN + c * 16, v);
           tmem_ld_wait();
-          const int n0 = tn * BN + c * 16;
-          if (m < p.M && n0 < p.N) {
-            T* dst = y + (int64_t)m * p.N + n0;
-            if (n0 + 16 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+          const int n0 = seg_n0 + c * 16;
+          if (m < p.M && n0 < sg.N) {
+            T* dst = y + (int64_t)m * p.ld_y + sg.col0 + n0;
+            if (n0 + 16 <= sg.N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
               struct alignas(16) Out { T e[8]; } o[2];
 #pragma unroll
               for (int q = 0; q < 2; ++q)
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                   float f = __uint_as_float(v[q * 8 + e]);
-                  if (p.bias) f += __ldg(p.bias + n0 + q * 8 + e);
+                  if (sg.bias) f += __ldg(sg.bias + n0 + q * 8 + e);
                   o[q].e[e] = from_f32<T>(f);
                 }
               reinterpret_cast<Out*>(dst)[0] = o[0];
@@ -396,9 +422,9 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
             } else {
 #pragma unroll
               for (int e = 0; e < 16; ++e)
-                if (n0 + e < p.N) {
+                if (n0 + e < sg.N) {
                   float f = __uint_as_float(v[e]);
-                  if (p.bias) f += __ldg(p.bias + n0 + e);
+                  if (sg.bias) f += __ldg(sg.bias + n0 + e);
                   dst[e] = from_f32<T>(f);
                 }
             }
@@ -420,18 +446,20 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
       const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
       const int total = my_tiles * num_kb;    // the CTA's (tile, k block) items in ring order
       const uint32_t b_stage = smem_u32(stage_base + (size_t)grp * stage_bytes + MT * kAStageBytes);
-      auto tile_n0 = [&](int i) { return ((blockIdx.x + (i / num_kb) * gridDim.x) / p.tiles_m) * BN; };
+      auto tile_tn = [&](int i) { return (int)((blockIdx.x + (i / num_kb) * gridDim.x) / p.tiles_m); };
       constexpr int RPL = 2;                  // rows per lane (second one only when BN > 128)
       const bool two = rows_per_warp > 32;
       RawRow<BITS> cur[RPL], nxt[RPL];
       auto fetch = [&](RawRow<BITS> (&dst)[RPL], int i) {
-        const int n0 = tile_n0(i) + row0, kb = i % num_kb;
+        const int tn = tile_tn(i), kb = i % num_kb;
+        const Seg& sg = seg_of(p, tn);
+        const int n0 = (tn - sg.tile0) * BN + row0;     // row inside the segment's weight
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
           const int rr = lane + 32 * r;
           if (r == 0 ? rr < rows_per_warp : (two && rr < rows_per_warp)) {
             const int n = n0 + rr;
-            fetch_row<BITS>(dst[r], p, n < p.N ? n : p.N - 1, kb);
+            fetch_row<BITS>(dst[r], p, sg.packed, n < sg.N ? n : sg.N - 1, kb);
           }
         }
       };
@@ -444,13 +472,15 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
           atomicExch(&g_vq_fused_status, 4);
           break;
         }
-        const int n0 = tile_n0(i) + row0, kb = i % num_kb;
+        const int tn = tile_tn(i), kb = i % num_kb;
+        const Seg& sg = seg_of(p, tn);
+        const int n0 = (tn - sg.tile0) * BN + row0;
         if constexpr (COPY && BITS != 0) {
 #pragma unroll
           for (int r = 0; r < RPL; ++r) {
             const int rr = lane + 32 * r;
             if (r == 0 ? rr < rows_per_warp : (two && rr < rows_per_warp))
-              emit_row_copy<BITS>(cur[r], p, n0 + rr < p.N, kb, b_stage, row0 + rr);
+              emit_row_copy<BITS>(cur[r], p, sg.cb_x, n0 + rr < sg.N, kb, b_stage, row0 + rr);
           }
           cp_async_arrive(&full_bar[grp]);  // every lane, also one without rows
         } else {
@@ -493,12 +523,14 @@ __global__ void codebook_cast_kernel(const __half* __restrict__ in, T* __restric
 
 // BN: a multiple of 16 in [16, 256] such that (waves of tiles) x BN -- the decode work of the
 // busiest SM -- is smallest; ties go to the wider tile (fewer x-tile re-reads).
-int pick_bn(int64_t N, int tiles_m, int mt, int sms) {
+int pick_bn(const FusedParams& p, int tiles_m, int mt, int sms) {
   int best_bn = 128;
   double best = 1e30;
   for (int bn = 256; bn >= 16; bn -= 16) {
     if (mt * bn > 512) continue;  // one accumulator buffer must fit TMEM
-    const int64_t tiles = (int64_t)tiles_m * ((N + bn - 1) / bn);
+    int64_t tiles_n = 0;
+    for (int i = 0; i < p.n_segs; ++i) tiles_n += (p.seg[i].N + bn - 1) / bn;   // a tile stays inside a segment
+    const int64_t tiles = (int64_t)tiles_m * tiles_n;
     const int64_t waves = (tiles + sms - 1) / sms;
     const double cost = (double)waves * bn;
     if (cost < best - 1e-9) { best = cost; best_bn = bn; }
@@ -541,8 +573,14 @@ int launch(const void* x, FusedParams p, cudaStream_t st) {
   auto kern = vq_gemm_fused_kernel<T, MT, BITS, COPY>;
   const int sms = sm_count();
   p.tiles_m = (p.M + BM * MT - 1) / (BM * MT);
-  p.BN = pick_bn(p.N, p.tiles_m, MT, sms);
-  p.tiles_n = (p.N + p.BN - 1) / p.BN;
+  p.BN = pick_bn(p, p.tiles_m, MT, sms);
+  p.tiles_n = 0;
+  for (int i = 0, col = 0; i < p.n_segs; ++i) {
+    p.seg[i].tile0 = p.tiles_n;
+    p.seg[i].col0 = col;
+    p.tiles_n += (p.seg[i].N + p.BN - 1) / p.BN;
+    col += p.seg[i].N;
+  }
   const int stage_bytes = MT * kAStageBytes + p.BN * 128;
   const int cap = max_dynamic_smem();
   // Narrow tiles have few gathers per stage and are bound by the latency of one decode; they get
@@ -676,7 +714,67 @@ int vq_gemm_fused(const npb_vq_weight* w, const void* codebook_x, const void* x,
     p.cb_x = codebook_x;
     p.clamp = (w->num_centroids != (1 << w->bits)) || p.groups_per_codebook > 0;
   }
+  p.n_segs = 1;
+  p.ld_y = (int)N;
+  p.seg[0] = Seg{p.packed, p.cb_x, p.centroids, bias, (int)N, 0, 0};
   return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(x, p, vbits, st) : launch_bits<__half>(x, p, vbits, st);
+}
+
+// Several plain weights applied to the same x in one launch (copy form only): y is [M, sum of Ns], weight i's
+// outputs in columns [sum of the Ns before it, + Ns[i]).  The weights must agree in index width, codebook size
+// and codebook layout; each brings its own codebook in the activation type.
+int vq_gemm_fused_grouped(const npb_vq_weight* ws, int n_weights, const void* const* codebooks_x, const int64_t* Ns,
+                          const float* const* biases, const void* x, int x_dtype, int64_t M, int64_t K, void* y,
+                          cudaStream_t st) {
+  if (ws == nullptr || codebooks_x == nullptr || Ns == nullptr || n_weights < 1 || n_weights > kMaxSegs)
+    return NPB_ERR_INVALID_ARG;
+  if (M < 0) return NPB_ERR_INVALID_ARG;
+  if (x_dtype != NPB_BF16 && x_dtype != NPB_F16) return NPB_ERR_UNSUPPORTED;
+  if (K == 0 || K % 64 != 0 || K >= (int64_t)1 << 31 || M >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
+  const npb_vq_weight& w0 = ws[0];
+  int64_t total_n = 0;
+  for (int i = 0; i < n_weights; ++i) {
+    const npb_vq_weight& w = ws[i];
+    if (int rc = validate_vq(&w, Ns[i], K)) return rc;
+    if (Ns[i] <= 0 || codebooks_x[i] == nullptr) return NPB_ERR_INVALID_ARG;
+    if (w.vector_len != 8 || w.res_packed != nullptr || w.row_scale != nullptr) return NPB_ERR_UNSUPPORTED;
+    if (w.bits != w0.bits || w.num_centroids != w0.num_centroids || w.cols_per_codebook != w0.cols_per_codebook)
+      return NPB_ERR_UNSUPPORTED;
+    if (w.bits != 16 && w.bits != 12 && w.bits != 8) return NPB_ERR_UNSUPPORTED;
+    if (!aligned_to(w.packed, index8_alignment(w.bits)) || !aligned_to(codebooks_x[i], 16) ||
+        !aligned_to(w.centroids, 16))
+      return NPB_ERR_ALIGNMENT;
+    total_n += Ns[i];
+  }
+  if (total_n >= (int64_t)1 << 31) return NPB_ERR_UNSUPPORTED;
+  if (M == 0) return NPB_OK;
+  if (x == nullptr || y == nullptr) return NPB_ERR_INVALID_ARG;
+  if (!aligned_to(x, 16)) return NPB_ERR_ALIGNMENT;
+  FusedParams p{};
+  p.packed = w0.packed;
+  p.packed_bytes = w0.packed_bytes;
+  p.centroids = static_cast<const __half*>(w0.centroids);
+  p.res_packed = w0.packed;
+  p.res_centroids = p.centroids;
+  p.row_scale = p.centroids;
+  p.bias = biases ? biases[0] : nullptr;
+  p.y = y;
+  p.bits = w0.bits;
+  p.num_centroids = w0.num_centroids;
+  p.groups_per_codebook = w0.cols_per_codebook > 0 ? w0.cols_per_codebook / 8 : 0;
+  if (p.groups_per_codebook % 8 != 0) return NPB_ERR_UNSUPPORTED;
+  p.cb_rows = w0.num_centroids *
+              (w0.cols_per_codebook > 0 ? (int)((K + w0.cols_per_codebook - 1) / w0.cols_per_codebook) : 1);
+  p.res_rows = 1;
+  p.M = (int)M; p.N = (int)total_n; p.K = (int)K;
+  p.cb_x = codebooks_x[0];
+  p.clamp = (w0.num_centroids != (1 << w0.bits)) || p.groups_per_codebook > 0;
+  p.n_segs = n_weights;
+  p.ld_y = (int)total_n;
+  for (int i = 0; i < n_weights; ++i)
+    p.seg[i] = Seg{ws[i].packed, codebooks_x[i], static_cast<const __half*>(ws[i].centroids),
+                   biases ? biases[i] : nullptr, (int)Ns[i], 0, 0};
+  return x_dtype == NPB_BF16 ? launch_bits<__nv_bfloat16>(x, p, w0.bits, st) : launch_bits<__half>(x, p, w0.bits, st);
 }
 
 }  // namespace npb

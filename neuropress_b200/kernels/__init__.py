@@ -279,6 +279,44 @@ def _vq_gemm_fused_copy(x, packed, centroids, bits, out_features, bias, ext):
     return y
 
 
+def vq_gemm_fused_grouped(x: torch.Tensor, weights: list[tuple], bits: int,
+                          cols_per_codebook: int = 0) -> torch.Tensor | None:
+    """Several plain VQ weights applied to the same ``x`` ``[M, K]`` by ONE launch of the copy form
+    of the tile-decode GEMM.  ``weights`` as in :func:`vq_gemv_grouped`; returns ``[M,
+    sum(out_features)]`` with the weights' outputs side by side, the same bits as one
+    :func:`vq_gemm_fused` call per weight -- or ``None`` when the kernel does not take this
+    combination."""
+    if (x.dim() != 2 or not 1 <= len(weights) <= 4 or bits not in (8, 12, 16)
+            or x.dtype not in (torch.float16, torch.bfloat16)):
+        return None
+    _cabi.require_cuda("vq_gemm_fused_grouped", x, *[t for w in weights for t in (w[0], w[1], w[3])])
+    lib = _cabi.load_library()
+    m, k = x.shape
+    n_w = len(weights)
+    structs = (_cabi.VQWeightStruct * n_w)()
+    ns = (ctypes.c_int64 * n_w)()
+    biases = (ctypes.c_void_p * n_w)()
+    cbs = (ctypes.c_void_p * n_w)()
+    keep = []
+    for i, (packed, cent, n, bias) in enumerate(weights):
+        if cent.dtype != torch.float16 or not cent.is_contiguous() or cent.shape[-1] != 8:
+            return None
+        structs[i] = _cabi.vq_struct(packed, cent, bits, cols_per_codebook=cols_per_codebook)
+        ns[i] = int(n)
+        biases[i] = None if bias is None else bias.data_ptr()
+        cbx = codebook_in_dtype(cent, x.dtype)
+        keep.append(cbx)
+        cbs[i] = cbx.data_ptr()
+    y = torch.empty((m, sum(int(w[2]) for w in weights)), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _launch("npb_vq_gemm_fused", lib.npb_vq_gemm_fused_grouped, structs, n_w, cbs, ns, biases,
+                     x.data_ptr(), _cabi.dtype_code(x.dtype), m, k, y.data_ptr(), _cabi.stream_ptr())
+    if rc in (2, 4):   # unsupported combination / alignment: the caller runs the members one by one
+        return None
+    _cabi.check(rc, "npb_vq_gemm_fused_grouped")
+    return y
+
+
 # Whether the mid-sized band runs the tile-decode GEMM (``npb_vq_gemm_fused``); when False it
 # runs the one-pass decode followed by the dense tensor-core GEMM.
 VQ_TILE_DECODE_GEMM = True

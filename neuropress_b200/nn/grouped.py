@@ -7,9 +7,10 @@ does.  :func:`group_shared_input_linears` rewires those modules, without touchin
 own ``forward`` code: each member is replaced by a :class:`GroupedLinear` whose first member
 ("leader") computes all outputs with ``npb_vq_gemv_grouped`` and hands the others their slices,
 and the norm in front of the group is replaced by a :class:`DeferredNorm` that passes its input
-through and lets the group's kernel normalise the activations while staging them.  Larger
-batches, or weights the grouped kernel does not take, fall back to the norm kernel and the
-members' own forwards -- same results, one launch each.
+through and lets the group's kernel normalise the activations while staging them.  From 17 rows
+to the end of the tile-decode band the norm runs as its own kernel and the members share one
+launch of ``npb_vq_gemm_fused_grouped``.  Larger batches, or weights the grouped kernels do not
+take, fall back to the norm kernel and the members' own forwards -- same results, one launch each.
 
 The group keys on the input tensor's identity between the leader's call and the followers'
 calls of the SAME forward; use it only for members that really receive the same tensor.
@@ -21,7 +22,7 @@ import torch
 from torch import nn
 
 from .np_rms_norm import NPRMSNorm
-from .np_vq_linear import NPVQLinear, _FUSED_BACKENDS, _SMALL_BATCH_MAX_TOKENS
+from .np_vq_linear import NPVQLinear, _FUSED_BACKENDS, _SMALL_BATCH_MAX_TOKENS, _TRITON_MAX_TOKENS
 
 __all__ = ["LinearGroup", "GroupedLinear", "DeferredNorm", "group_shared_input_linears"]
 
@@ -51,6 +52,28 @@ class LinearGroup:
                         for m in self.members)
                 and m0._small_batch_ok(x2, max(x2.shape[0], 3)))
 
+    def _tile_fusable(self, x2: torch.Tensor) -> bool:
+        """The members would all take the copy form of the tile-decode GEMM for these rows (the
+        conditions of ``NPVQLinear._forward_triton`` and of ``kernels.vq_gemm_fused``)."""
+        from .. import kernels
+
+        m0 = self.members[0]
+        rows = x2.shape[0]
+        return (kernels.VQ_TILE_DECODE_GEMM and kernels.VQ_COPY_FORM and len(self.members) > 1
+                and _SMALL_BATCH_MAX_TOKENS < rows <= _TRITON_MAX_TOKENS and m0.backend in _FUSED_BACKENDS
+                and x2.dtype in (torch.bfloat16, torch.float16) and m0.vector_len == 8
+                and m0.bits in (8, 12, 16) and m0.in_features % 64 == 0
+                and not (m0.cols_per_codebook and m0.cols_per_codebook % 64)
+                and all(m.column_perm is None and m.residual_indices is None and m.row_scale is None
+                        and m.packed_indices.data_ptr() % 16 == 0 for m in self.members))
+
+    def _split(self, y: torch.Tensor, leading) -> list[torch.Tensor]:
+        outs, c = [], 0
+        for m in self.members:
+            outs.append(y[:, c:c + m.out_features].reshape(*leading, m.out_features))
+            c += m.out_features
+        return outs
+
     def _norm_weight(self, dtype: torch.dtype) -> torch.Tensor:
         w = self.norm.weight
         if self._norm_w is None or self._norm_w.dtype != dtype or self._norm_w.device != w.device \
@@ -71,12 +94,14 @@ class LinearGroup:
                                         None if self.norm is None else self._norm_weight(x2.dtype),
                                         0.0 if self.norm is None else self.norm.eps)
             if y is not None:
-                outs, c = [], 0
-                for m in self.members:
-                    outs.append(y[:, c:c + m.out_features].reshape(*leading, m.out_features))
-                    c += m.out_features
-                return outs
+                return self._split(y, leading)
         xn = x if self.norm is None else self.norm(x)       # one norm launch, shared by the members
+        xn2 = xn.reshape(-1, k)
+        if self._tile_fusable(xn2):
+            weights = [(m.packed_indices, m.proxy.centroids, m.out_features, m._bias32()) for m in self.members]
+            y = kernels.vq_gemm_fused_grouped(xn2.contiguous(), weights, m0.bits, m0.cols_per_codebook)
+            if y is not None:
+                return self._split(y, leading)
         return [m(xn) for m in self.members]
 
     def output(self, index: int, x: torch.Tensor) -> torch.Tensor:

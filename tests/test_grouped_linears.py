@@ -8,6 +8,7 @@ from torch import nn
 
 import oracle
 from helpers import assert_output_close
+from neuropress_b200 import _cabi
 from neuropress_b200.nn import (DeferredNorm, GroupedLinear, NPRMSNorm, NPVQLinear, VQProxy,
                                 group_shared_input_linears)
 from synthetic import make_activations, make_vq_layer
@@ -87,10 +88,29 @@ def test_grouping_pass_structure_and_fallbacks(monkeypatch):
                         torch.zeros(x.shape[0], n, dtype=x.dtype))
     layer.self_attn(layer.input_layernorm(x))
     assert seen == ["norm", "gemv", "gemv", "gemv"]
+    # 17 rows to the end of the tile-decode band: one norm launch, then one grouped GEMM launch
+    seen.clear()
+
+    def fake_tile_grouped(x, weights, bits, cpc=0):
+        seen.append(("tile", len(weights)))
+        return torch.zeros(x.shape[0], sum(w[2] for w in weights), dtype=x.dtype)
+
+    monkeypatch.setattr(kernels, "vq_gemm_fused_grouped", fake_tile_grouped)
+    x40 = torch.zeros(40, 1024, dtype=torch.bfloat16)
+    q, k, v = layer.self_attn(layer.input_layernorm(x40))
+    assert (q.shape, k.shape, v.shape) == ((40, 256), (40, 64), (40, 64))
+    assert seen == ["norm", ("tile", 3)]
+    # the grouped GEMM declines: the members' own tile-decode GEMMs
+    seen.clear()
+    monkeypatch.setattr(kernels, "vq_gemm_fused_grouped", lambda *a, **k: None)
+    monkeypatch.setattr(kernels, "vq_gemm_fused", lambda x, p, c, b, n, bias, **e: seen.append("fused") or
+                        torch.zeros(x.shape[0], n, dtype=x.dtype))
+    layer.mlp(layer.post_attention_layernorm(x40))
+    assert seen == ["norm", "fused", "fused"]
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows", [1, 5, 16, 40])
+@pytest.mark.parametrize("rows", [1, 5, 16, 17, 40, 130, 384, 400])
 def test_grouped_launch_matches_the_ungrouped_modules(rows):
     dev = torch.device("cuda", 0)
     data = {}
@@ -131,3 +151,48 @@ def test_grouped_launch_without_norm_is_bit_identical_to_single_launches():
         for m in mods:
             assert torch.equal(y[:, c:c + m.out_features], m(x))
             c += m.out_features
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,nc", [(16, 4096), (12, 4096), (8, 256)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_grouped_tile_decode_gemm_is_bit_identical_to_single_launches(bits, nc, dtype):
+    """``npb_vq_gemm_fused_grouped``: ragged member widths (tiles padded per member, odd column
+    offsets in y), with and without bias, every row band of the kernel."""
+    from neuropress_b200 import kernels
+
+    dev = torch.device("cuda", 0)
+    mods = []
+    for seed, n in enumerate((264, 72, 1000, 3), start=1):
+        d = make_vq_layer(n, 2048, num_centroids=nc, bits=bits, seed=seed, bias=seed % 2 == 1)
+        layer = NPVQLinear(VQProxy(d.centroids), d.packed, bits, n, 2048, 8, backend="cuda", bias=d.bias)
+        layer.proxy.to(dev)
+        mods.append(layer.to(dev))
+    weights = [(m.packed_indices, m.proxy.centroids, m.out_features, m._bias32()) for m in mods]
+    for rows in (17, 64, 129, 300, 384):
+        x = make_activations(rows, 2048, dtype, seed=rows).to(dev)
+        for n_w in (4, 2, 1):
+            y = kernels.vq_gemm_fused_grouped(x, weights[:n_w], bits, 0)
+            assert y is not None and y.shape == (rows, sum(m.out_features for m in mods[:n_w]))
+            c = 0
+            for m in mods[:n_w]:
+                single = kernels.vq_gemm_fused(x, m.packed_indices, m.proxy.centroids, bits, m.out_features,
+                                               m._bias32())
+                assert torch.equal(y[:, c:c + m.out_features], single)
+                c += m.out_features
+    assert _cabi.gemm_device_status() == 0
+
+
+@pytest.mark.gpu
+def test_grouped_tile_decode_gemm_declines_what_it_does_not_take():
+    from neuropress_b200 import kernels
+
+    dev = torch.device("cuda", 0)
+    a = make_vq_layer(64, 1024, num_centroids=4096, bits=16, seed=1)
+    b = make_vq_layer(64, 1024, num_centroids=1024, bits=16, seed=2)
+    x = make_activations(32, 1024, torch.bfloat16, seed=3).to(dev)
+    wa = (a.packed.to(dev), a.centroids.to(dev), 64, None)
+    wb = (b.packed.to(dev), b.centroids.to(dev), 64, None)
+    assert kernels.vq_gemm_fused_grouped(x, [wa, wb], 16, 0) is None          # another codebook size
+    assert kernels.vq_gemm_fused_grouped(x, [wa] * 5, 16, 0) is None          # more than four members
+    assert kernels.vq_gemm_fused_grouped(x.float(), [wa, wa], 16, 0) is None  # fp32 activations
