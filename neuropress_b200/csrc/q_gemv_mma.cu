@@ -229,6 +229,208 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_gemv_mma_kernel(MmaArgs a) {
   }
 }
 
+// ---- 3-8 activation rows: all eight columns of the mma carry an activation row ---------------
+// The block-diagonal operand above spends an mma column per (32-block, activation row) pair: eight
+// rows cost four mmas per A fragment, and mma.sync issue (one m16n8k16 per ~11 clocks per SM on
+// sm_100) is what bounds the kernel.  Here the four lanes of a quad first exchange code words so
+// that, for each 32-block j of the step, lane t holds word t of block j (rows g and g + 8): the 16
+// k slots of an mma then all belong to ONE 32-block, its D tile is that block's partial dot
+// products for 16 weight rows x 8 activation rows, and scale / zero-point are applied to D once
+// per block: two mmas per block whatever the row count (256 weights per mma at 8 rows).
+//
+// rot4(v, s)[i] = v[(i + s) & 3] for a run-time s (two conditional stages of selects).
+__device__ __forceinline__ void rot4(uint32_t (&v)[4], int s) {
+  uint32_t a0 = (s & 1) ? v[1] : v[0], a1 = (s & 1) ? v[2] : v[1], a2 = (s & 1) ? v[3] : v[2],
+           a3 = (s & 1) ? v[0] : v[3];
+  v[0] = (s & 2) ? a2 : a0;
+  v[1] = (s & 2) ? a3 : a1;
+  v[2] = (s & 2) ? a0 : a2;
+  v[3] = (s & 2) ? a1 : a3;
+}
+
+// In: lane t of a quad holds w[u] = word u of block t.  Out: w[j] = word t of block j.
+__device__ __forceinline__ void quad_transpose(uint32_t (&w)[4], int t, int lane) {
+  rot4(w, t);                                  // w[r] = word (t + r) & 3: what the lane r places back reads
+  const int base = lane & ~3;
+  uint32_t r1 = __shfl_sync(0xffffffffu, w[1], base | ((t - 1) & 3));   // block (t-1)&3, word t
+  uint32_t r2 = __shfl_sync(0xffffffffu, w[2], base | ((t - 2) & 3));
+  uint32_t r3 = __shfl_sync(0xffffffffu, w[3], base | ((t - 3) & 3));
+  // v[i] = word t of block (t + i) & 3; block j sits at i = (j - t) & 3
+  w[1] = r3; w[2] = r2; w[3] = r1;
+  rot4(w, (4 - t) & 3);
+}
+
+template <typename T, int WARPS, bool ZP>
+__global__ void __launch_bounds__(WARPS * 32, 1) q4_gemv_mma_quad_kernel(MmaArgs a, int gs_shift, int chunk) {
+  constexpr int MR = 8;
+  constexpr int kThreads = WARPS * 32;
+  constexpr uint32_t kMagic = std::is_same<T, __nv_bfloat16>::value ? 0x43004300u : 0x64006400u;
+  constexpr float kOffset = std::is_same<T, __nv_bfloat16>::value ? 128.f : 1024.f;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int K = a.K;
+  // xs[step][h][block j][word t][activation row g][4 values]: the 32 lanes of an mma read 256
+  // consecutive bytes.  xsum[32-block][activation row].  red[WARPS][chunk][16][MR]: the warps' partial
+  // tiles of `chunk` row blocks meet at one barrier, not one per row block.
+  T* xs = reinterpret_cast<T*>(smem);
+  float* xsum = reinterpret_cast<float*>(xs + (size_t)MR * K);
+  float* red = xsum + (size_t)MR * (K / 32);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int groups = K >> gs_shift;
+  const int spw = K / 128 / WARPS;
+  const int n_blocks = (a.N + 15) / 16;
+  const int my_blocks = blockIdx.x < n_blocks ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int total = my_blocks * spw;
+
+  // Load cursor: (row block, step of this warp) of the next request; the row offsets (32-bit: the
+  // host checks the sizes) change once per row block, nothing is divided per step.  Scales and zero
+  // points stay as loaded (one register per 16-bit load): packing them where they are loaded would
+  // make the warp wait for the loads right there instead of kPrefetch steps later.
+  struct Step { uint4 ca, cb; unsigned short sA, sB, zA, zB; };
+  const unsigned short* scale_u = reinterpret_cast<const unsigned short*>(a.scale);
+  const unsigned short* zp_u = reinterpret_cast<const unsigned short*>(a.zp);
+  int l_rb = blockIdx.x, l_si = 0;
+  uint32_t l_codeA = 0, l_codeB = 0, l_grpA = 0, l_grpB = 0;
+  auto load_next = [&](Step& st) {
+    if (l_si == 0) {
+      const int rA = l_rb * 16 + g < a.N ? l_rb * 16 + g : a.N - 1;
+      const int rB = l_rb * 16 + g + 8 < a.N ? l_rb * 16 + g + 8 : a.N - 1;
+      l_codeA = (uint32_t)rA * (uint32_t)(K >> 1) + (uint32_t)t * 16u;
+      l_codeB = (uint32_t)rB * (uint32_t)(K >> 1) + (uint32_t)t * 16u;
+      l_grpA = (uint32_t)rA * (uint32_t)groups;
+      l_grpB = (uint32_t)rB * (uint32_t)groups;
+    }
+    const int kb = warp + l_si * WARPS;
+    st.ca = __ldg(reinterpret_cast<const uint4*>(a.codes + l_codeA + kb * 64));
+    st.cb = __ldg(reinterpret_cast<const uint4*>(a.codes + l_codeB + kb * 64));
+    const uint32_t grp = (uint32_t)(kb * 128 + t * 32) >> gs_shift;
+    st.sA = __ldg(scale_u + l_grpA + grp);
+    st.sB = __ldg(scale_u + l_grpB + grp);
+    if constexpr (ZP) {
+      st.zA = __ldg(zp_u + l_grpA + grp);
+      st.zB = __ldg(zp_u + l_grpB + grp);
+    }
+    if (++l_si == spw) { l_si = 0; l_rb += (int)gridDim.x; }
+  };
+
+  Step ring[kPrefetch];
+#pragma unroll
+  for (int p = 0; p < kPrefetch; ++p)
+    if (p < total) load_next(ring[p]);
+
+  {
+    const T* x = static_cast<const T*>(a.x);
+    for (int i = tid; i < MR * (K / 32); i += kThreads) {
+      const int m = i % MR, blk = i / MR;     // 32-block blk = (step, block tb)
+      const int step = blk >> 2, tb = blk & 3;
+      float s = 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        struct alignas(16) V8 { T v[8]; } v, p;
+        if (m < a.M) {
+          v = *reinterpret_cast<const V8*>(x + (size_t)m * K + blk * 32 + u * 8);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v.v[e] = from_f32<T>(0.f);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { p.v[perm8(e)] = v.v[e]; s += to_f32(v.v[e]); }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          *reinterpret_cast<uint2*>(xs + (((((size_t)step * 2 + h) * 4 + tb) * 4 + u) * 8 + m) * 4) =
+              *reinterpret_cast<const uint2*>(&p.v[4 * h]);
+      }
+      xsum[i] = s;
+    }
+  }
+  __syncthreads();
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};   // (row g, m 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+  const int quad = lane & ~3;
+  const T* xs_lane = xs + (t * 8 + g) * 4;            // + step * 1024 + (h * 4 + j) * 128
+  const float* xsum_lane = xsum + 2 * t;              // + (step * 4 + j) * MR
+  int c_rb = blockIdx.x, c_si = 0, c_blk = 0;         // compute cursor
+  for (int base = 0; base < total; base += kPrefetch) {
+#pragma unroll
+    for (int p = 0; p < kPrefetch; ++p) {
+      const int q = base + p;
+      if (q >= total) break;
+      const Step cur = ring[p];
+      if (q + kPrefetch < total) load_next(ring[p]);
+      const int kb = warp + c_si * WARPS;
+      uint32_t wa[4] = {cur.ca.x, cur.ca.y, cur.ca.z, cur.ca.w};
+      uint32_t wb[4] = {cur.cb.x, cur.cb.y, cur.cb.z, cur.cb.w};
+      quad_transpose(wa, t, lane);
+      quad_transpose(wb, t, lane);
+      const uint32_t s2 = (uint32_t)cur.sA | ((uint32_t)cur.sB << 16);
+      const uint32_t z2 = ZP ? ((uint32_t)cur.zA | ((uint32_t)cur.zB << 16)) : 0x48004800u;   // 8.0, 8.0
+      const T* xb = xs_lane + (size_t)kb * 1024;
+      const float* xsb = xsum_lane + kb * (4 * MR);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float d[4];
+        uint32_t pa[4], pb[4];
+        pa[0] = (wa[j] & 0x000f000fu) | kMagic;
+        pb[0] = (wb[j] & 0x000f000fu) | kMagic;
+#pragma unroll
+        for (int i = 1; i < 4; ++i) {
+          pa[i] = ((wa[j] >> (4 * i)) & 0x000f000fu) | kMagic;
+          pb[i] = ((wb[j] >> (4 * i)) & 0x000f000fu) | kMagic;
+        }
+        {
+          const uint32_t af[4] = {pa[0], pb[0], pa[1], pb[1]};
+          const uint2 bv = *reinterpret_cast<const uint2*>(xb + j * 128);
+          mma16816_first<T>(d, af, bv.x, bv.y);
+        }
+        {
+          const uint32_t af[4] = {pa[2], pb[2], pa[3], pb[3]};
+          const uint2 bv = *reinterpret_cast<const uint2*>(xb + (4 + j) * 128);
+          mma16816<T>(d, af, bv.x, bv.y);
+        }
+        const uint32_t sj = __shfl_sync(0xffffffffu, s2, quad | j);
+        const uint32_t zj = ZP ? __shfl_sync(0xffffffffu, z2, quad | j) : z2;
+        const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(&sj));
+        const float2 zc = __half22float2(*reinterpret_cast<const __half2*>(&zj));
+        const float2 xsm = *reinterpret_cast<const float2*>(xsb + j * MR);
+        const float ca = kOffset + zc.x, cb = kOffset + zc.y;
+        acc[0] = fmaf(sc.x, d[0] - ca * xsm.x, acc[0]);
+        acc[1] = fmaf(sc.x, d[1] - ca * xsm.y, acc[1]);
+        acc[2] = fmaf(sc.y, d[2] - cb * xsm.x, acc[2]);
+        acc[3] = fmaf(sc.y, d[3] - cb * xsm.y, acc[3]);
+      }
+
+      if (++c_si == spw) {
+        // Row block finished for this warp: every lane holds four distinct outputs.
+        c_si = 0;
+        float* rbuf = red + ((size_t)warp * chunk + c_blk) * 16 * MR;
+        *reinterpret_cast<float2*>(rbuf + g * MR + 2 * t) = make_float2(acc[0], acc[1]);
+        *reinterpret_cast<float2*>(rbuf + (g + 8) * MR + 2 * t) = make_float2(acc[2], acc[3]);
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        ++c_blk;
+        if (c_blk == chunk || q + 1 == total) {
+          // Every warp reaches this after the same steps.  Sum the warps' tiles of the chunk's row blocks.
+          __syncthreads();
+          for (int i = tid; i < c_blk * 16 * MR; i += kThreads) {
+            const int b = i / (16 * MR), rm = i - b * (16 * MR);
+            const int r = rm / MR, m = rm - r * MR;
+            const int n = (c_rb + b * (int)gridDim.x) * 16 + r;
+            if (n < a.N && m < a.M) {
+              float v = 0.f;
+#pragma unroll
+              for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * chunk + b) * 16 * MR + rm];
+              if (a.bias) v += __ldg(a.bias + n);
+              static_cast<T*>(a.y)[(size_t)m * a.N + n] = from_f32<T>(v);
+            }
+          }
+          c_rb += c_blk * (int)gridDim.x;
+          c_blk = 0;
+          if (q + 1 < total) __syncthreads();   // the next chunk overwrites red
+        }
+      }
+    }
+  }
+}
+
 // ---- 1-2 activation rows: the decode band proper ---------------------------------------------
 // One persistent CTA per SM owns a contiguous range of output rows; warp w owns the K slice
 // [w*K/WARPS, (w+1)*K/WARPS) for all of them, so it stages only its own slice of the
@@ -270,7 +472,12 @@ q4_gemv_mma_rows8_kernel(MmaArgs a, int rows_per_cta, int gs_shift) {
   const int groups = K >> gs_shift;
   const int k_lane = warp * KS + t * 32;    // first k of this lane's block in step A of pair 0
 
-  struct Step { uint4 ca, cb; __half2 s, z; };
+  // Scales / zero points stay as loaded (one register per 16-bit load): packing them here would make
+  // the warp wait for the loads where they are issued instead of PF steps later.
+  struct Step { uint4 ca, cb; unsigned short sa, sb, za, zb; };
+  const unsigned short* scale_u = reinterpret_cast<const unsigned short*>(a.scale);
+  const unsigned short* zp_u = reinterpret_cast<const unsigned short*>(a.zp);
+  const bool has_zp = a.zp != nullptr;
   // load cursor: (row group, pair) of the next step to request
   int l_rg = 0, l_pr = 0;
   auto load_next = [&](Step& st) {
@@ -282,9 +489,14 @@ q4_gemv_mma_rows8_kernel(MmaArgs a, int rows_per_cta, int gs_shift) {
     st.cb = __ldg(reinterpret_cast<const uint4*>(p + 64));
     const size_t sidx = (size_t)row * groups;
     const int ga = kA >> gs_shift, gb = (kA + 128) >> gs_shift;
-    st.s = __halves2half2(__ldg(a.scale + sidx + ga), __ldg(a.scale + sidx + gb));
-    st.z = a.zp ? __halves2half2(__ldg(a.zp + sidx + ga), __ldg(a.zp + sidx + gb))
-                : __float2half2_rn(8.f);
+    st.sa = __ldg(scale_u + sidx + ga);
+    st.sb = __ldg(scale_u + sidx + gb);
+    if (has_zp) {
+      st.za = __ldg(zp_u + sidx + ga);
+      st.zb = __ldg(zp_u + sidx + gb);
+    } else {
+      st.za = st.zb = 0x4800;   // 8.0
+    }
     if (++l_pr == pairs) { l_pr = 0; ++l_rg; }
   };
 
@@ -371,7 +583,8 @@ q4_gemv_mma_rows8_kernel(MmaArgs a, int rows_per_cta, int gs_shift) {
           }
         }
       }
-      const float2 sc = __half22float2(cur.s), zc = __half22float2(cur.z);
+      const float2 sc = make_float2(__half2float(__ushort_as_half(cur.sa)), __half2float(__ushort_as_half(cur.sb)));
+      const float2 zc = make_float2(__half2float(__ushort_as_half(cur.za)), __half2float(__ushort_as_half(cur.zb)));
       const int xb = c_pr * 8 + t;   // 32-block index of step A inside the slice; step B is +4
 #pragma unroll
       for (int m = 0; m < MR; ++m) {
@@ -464,8 +677,46 @@ int launch_warps(const MmaArgs& a, cudaStream_t st) {
   return launch_mma<T, MP, 4>(a, st);
 }
 
+template <typename T, int WARPS>
+int launch_quad(const MmaArgs& a, cudaStream_t st) {
+  const size_t fixed = (size_t)8 * a.K * sizeof(T) + (size_t)8 * (a.K / 32) * 4;
+  const size_t per_block = (size_t)WARPS * 16 * 8 * 4;    // the warps' partial tiles of one row block
+  const size_t cap_smem = (size_t)max_dynamic_smem();
+  if (fixed + per_block > cap_smem) return NPB_ERR_UNSUPPORTED;
+  const int n_blocks_all = (a.N + 15) / 16;
+  int chunk = (n_blocks_all + sm_count() - 1) / sm_count();   // row blocks per CTA
+  const size_t room = (cap_smem - fixed) / per_block;
+  if ((size_t)chunk > room) chunk = (int)room;
+  if (chunk > 16) chunk = 16;
+  const size_t smem = fixed + per_block * chunk;
+  auto kern = a.zp ? q4_gemv_mma_quad_kernel<T, WARPS, true> : q4_gemv_mma_quad_kernel<T, WARPS, false>;
+  int per_sm = 0;
+  if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), WARPS * 32, smem, &per_sm)) return rc;
+  if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
+  int gs_shift = 0;
+  while ((1 << gs_shift) < a.group_size) ++gs_shift;
+  if ((1 << gs_shift) != a.group_size) return NPB_ERR_UNSUPPORTED;      // power-of-two groups only
+  if ((int64_t)a.N * (a.K >> 1) >= ((int64_t)1 << 31)) return NPB_ERR_UNSUPPORTED;   // 32-bit row offsets
+  const int n_blocks = (a.N + 15) / 16;
+  const int cap = sm_count() * per_sm;
+  kern<<<n_blocks < cap ? n_blocks : cap, WARPS * 32, smem, st>>>(a, gs_shift, chunk);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
+template <typename T>
+int run_quad(const MmaArgs& a, cudaStream_t st) {
+  if (a.K % 2048 == 0) return launch_quad<T, 16>(a, st);
+  if (a.K % 1024 == 0) return launch_quad<T, 8>(a, st);
+  return launch_quad<T, 4>(a, st);
+}
+
 template <typename T>
 int run_mma(const MmaArgs& a, cudaStream_t st) {
+  if (a.M >= 3) {   // every mma column carries a row: a quarter of the mmas at 8 rows
+    const int rc = run_quad<T>(a, st);
+    if (rc != NPB_ERR_UNSUPPORTED) return rc;
+  }
   const int mp = (a.M + 1) / 2;
   switch (mp) {
     case 1: return launch_warps<T, 1>(a, st);

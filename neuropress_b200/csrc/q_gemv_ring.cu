@@ -327,9 +327,218 @@ int launch_ring(RingArgs a, cudaStream_t st) {
   return NPB_OK;
 }
 
+// ---- 3-8 activation rows ------------------------------------------------------------------------
+// The same ring, with every column of the mma carrying an activation row.  A stage holds SIXTEEN
+// weight rows (A rows g and g + 8), each row a bulk copy of its own at a stride of K/2 + 16 bytes,
+// so that lane (g, t) can read ONE code word -- word t of the 32-block j of its rows -- without a
+// bank conflict: the 16 k slots of an mma then belong to one 32-block, whose D tile (16 weight rows
+// x 8 activation rows) takes that block's scale and zero-point once.  Two mmas per block, whatever
+// the row count: 256 weights per mma at 8 rows, against 64 with a block-diagonal operand.
+// The activation fragments and block sums of the warp's K slice (256 wide) stay in registers.
+constexpr int kRows16 = 16;
+
+template <typename T, bool ZP>
+__global__ void __launch_bounds__(kThreads, 1) q4_gemv_ring8_kernel(RingArgs a) {
+  constexpr uint32_t kMagic = std::is_same<T, __nv_bfloat16>::value ? 0x43004300u : 0x64006400u;
+  constexpr float kOffset = std::is_same<T, __nv_bfloat16>::value ? 128.f : 1024.f;
+  constexpr int STEPS = 2;                  // 128-wide steps of a warp's K slice (K = 4096)
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int K = a.K;
+  const int KS = K / kCW;                   // 256
+  const int groups = K >> a.gs_shift;
+  const int row_bytes = K / 2, row_stride = row_bytes + 16;
+  const int sc_row = groups * 2, sc_stride = sc_row + 16;
+  const int sc_off = kRows16 * row_stride;                   // scales of a stage
+  const int zp_off = sc_off + kRows16 * sc_stride;           // zero points
+  const int stage_bytes = zp_off + (ZP ? kRows16 * sc_stride : 0);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+  uint64_t* empty = full + kMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
+  uint8_t* ring = smem + 256;
+  float* part = reinterpret_cast<float*>(ring + (size_t)a.stages * stage_bytes);   // [kCW][rows_per_cta][8]
+
+  const int r0 = blockIdx.x * a.rows_per_cta;
+  const int r1 = r0 + a.rows_per_cta < a.N ? r0 + a.rows_per_cta : a.N;
+  const int n_rg = r1 > r0 ? (r1 - r0 + kRows16 - 1) / kRows16 : 0;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kCW);
+    }
+    fence_barrier_init();
+  }
+  __syncthreads();
+
+  if (warp == kCW) {
+    // ================= producer: lane r issues the copies of row r of every stage =================
+    int s = 0;
+    uint32_t ph = 0;
+    const uint32_t tx = (uint32_t)(kRows16 * (row_bytes + sc_row * (ZP ? 2 : 1)));
+    for (int rg = 0; rg < n_rg; ++rg) {
+      const bool ok = mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag, a.wait_ns, 32u);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) atomicExch(&g_q_ring_status, 3);
+        break;
+      }
+      uint8_t* st = ring + (size_t)s * stage_bytes;
+      if (lane == 0) mbar_arrive_expect_tx(&full[s], tx);
+      __syncwarp();   // the expectation is posted before any copy can complete
+      if (lane < kRows16) {
+        // rows past the end re-read the last row (always mapped); their sums are never stored
+        const int row = r0 + rg * kRows16 + lane < r1 ? r0 + rg * kRows16 + lane : r1 - 1;
+        bulk_g2s(st + (size_t)lane * row_stride, a.codes + (size_t)row * row_bytes, (uint32_t)row_bytes, &full[s]);
+        bulk_g2s(st + sc_off + (size_t)lane * sc_stride, a.scale + (size_t)row * groups, (uint32_t)sc_row, &full[s]);
+        if (ZP)
+          bulk_g2s(st + zp_off + (size_t)lane * sc_stride, a.zp + (size_t)row * groups, (uint32_t)sc_row, &full[s]);
+      }
+      if (++s == a.stages) { s = 0; ph ^= 1; }
+    }
+  } else {
+    // ================= consumers =================
+    // Activation fragments of this warp's K slice, straight from global memory (read once): for
+    // (step S, block j) the lane's chunk is word t of that block of activation row g; values
+    // 0,4,1,5 feed the first mma of the block, 2,6,3,7 the second (the order one mask extracts
+    // nibble pairs from a code word).  Block sums for the activation rows 2t, 2t+1 of the D tile.
+    uint2 bfrag[STEPS][4][2];
+    float2 xsum[STEPS][4];
+    {
+      const T* x = static_cast<const T*>(a.x);
+#pragma unroll
+      for (int S = 0; S < STEPS; ++S)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          struct alignas(16) V8 { T v[8]; } v, pv;
+          if (g < a.M) {
+            v = *reinterpret_cast<const V8*>(x + (size_t)g * K + warp * KS + S * 128 + j * 32 + t * 8);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v.v[e] = from_f32<T>(0.f);
+          }
+          float sum = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { pv.v[perm8(e)] = v.v[e]; sum += to_f32(v.v[e]); }
+          bfrag[S][j][0] = *reinterpret_cast<const uint2*>(&pv.v[0]);
+          bfrag[S][j][1] = *reinterpret_cast<const uint2*>(&pv.v[4]);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);      // the block's sum for activation row g
+          xsum[S][j].x = __shfl_sync(0xffffffffu, sum, (2 * t) * 4);
+          xsum[S][j].y = __shfl_sync(0xffffffffu, sum, (2 * t + 1) * 4);
+        }
+    }
+
+    int s = 0;
+    uint32_t ph = 0;
+    const int kbyte = (warp * KS) >> 1;               // this warp's slice inside a code row
+    const int gbase = (warp * KS) >> a.gs_shift;      // first scale group of the slice
+    for (int rg = 0; rg < n_rg; ++rg) {
+      const bool got = mbar_wait_bounded(&full[s], ph, abort_flag, a.wait_ns);
+      if (!__all_sync(0xffffffffu, got)) {
+        atomicExch(&g_q_ring_status, 4);
+        break;
+      }
+      const uint8_t* st = ring + (size_t)s * stage_bytes;
+      const uint8_t* rowA = st + (size_t)g * row_stride + kbyte + t * 4;
+      const uint8_t* rowB = rowA + 8 * row_stride;
+      const unsigned short* sA = reinterpret_cast<const unsigned short*>(st + sc_off + (size_t)g * sc_stride) + gbase;
+      const unsigned short* sB = reinterpret_cast<const unsigned short*>(st + sc_off + (size_t)(g + 8) * sc_stride) + gbase;
+      const unsigned short* zA = reinterpret_cast<const unsigned short*>(st + zp_off + (size_t)g * sc_stride) + gbase;
+      const unsigned short* zB = reinterpret_cast<const unsigned short*>(st + zp_off + (size_t)(g + 8) * sc_stride) + gbase;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};   // (row g, m 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+#pragma unroll
+      for (int S = 0; S < STEPS; ++S) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t wa = *reinterpret_cast<const uint32_t*>(rowA + S * 64 + j * 16);
+          const uint32_t wb = *reinterpret_cast<const uint32_t*>(rowB + S * 64 + j * 16);
+          uint32_t pa[4], pb[4];
+          pa[0] = (wa & 0x000f000fu) | kMagic;
+          pb[0] = (wb & 0x000f000fu) | kMagic;
+#pragma unroll
+          for (int i = 1; i < 4; ++i) {
+            pa[i] = ((wa >> (4 * i)) & 0x000f000fu) | kMagic;
+            pb[i] = ((wb >> (4 * i)) & 0x000f000fu) | kMagic;
+          }
+          float d[4];
+          {
+            const uint32_t af[4] = {pa[0], pb[0], pa[1], pb[1]};
+            mma16816_first<T>(d, af, bfrag[S][j][0].x, bfrag[S][j][0].y);
+          }
+          {
+            const uint32_t af[4] = {pa[2], pb[2], pa[3], pb[3]};
+            mma16816<T>(d, af, bfrag[S][j][1].x, bfrag[S][j][1].y);
+          }
+          const int grp = (S * 128 + j * 32) >> a.gs_shift;
+          const float sa = __half2float(__ushort_as_half(sA[grp])), sb = __half2float(__ushort_as_half(sB[grp]));
+          float ca = kOffset + 8.f, cb = kOffset + 8.f;
+          if (ZP) {
+            ca = kOffset + __half2float(__ushort_as_half(zA[grp]));
+            cb = kOffset + __half2float(__ushort_as_half(zB[grp]));
+          }
+          acc[0] = fmaf(sa, d[0] - ca * xsum[S][j].x, acc[0]);
+          acc[1] = fmaf(sa, d[1] - ca * xsum[S][j].y, acc[1]);
+          acc[2] = fmaf(sb, d[2] - cb * xsum[S][j].x, acc[2]);
+          acc[3] = fmaf(sb, d[3] - cb * xsum[S][j].y, acc[3]);
+        }
+      }
+      // this warp is done with the stage: hand it back before the partial sums are written
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      if (++s == a.stages) { s = 0; ph ^= 1; }
+      const int r = rg * kRows16 + g;   // < rows_per_cta (a multiple of 16)
+      float* pw = part + ((size_t)warp * a.rows_per_cta + r) * 8 + 2 * t;
+      *reinterpret_cast<float2*>(pw) = make_float2(acc[0], acc[1]);
+      *reinterpret_cast<float2*>(pw + 8 * 8) = make_float2(acc[2], acc[3]);
+    }
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  for (int i = tid; i < (r1 - r0) * 8; i += kThreads) {
+    const int r = i >> 3, m = i & 7;
+    if (m < a.M) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kCW; ++w) v += part[((size_t)w * a.rows_per_cta + r) * 8 + m];
+      const int n = r0 + r;
+      if (a.bias) v += __ldg(a.bias + n);
+      static_cast<T*>(a.y)[(size_t)m * a.N + n] = from_f32<T>(v);
+    }
+  }
+}
+
+template <typename T>
+int launch_ring8(RingArgs a, cudaStream_t st) {
+  const int sms = sm_count();
+  int rows_per_cta = (a.N + sms - 1) / sms;
+  rows_per_cta = (rows_per_cta + kRows16 - 1) / kRows16 * kRows16;
+  a.rows_per_cta = rows_per_cta;
+  const int grid = (a.N + rows_per_cta - 1) / rows_per_cta;
+  const int K = a.K, groups = K >> a.gs_shift;
+  const size_t stage_bytes = (size_t)kRows16 * (K / 2 + 16) + (size_t)kRows16 * (groups * 2 + 16) * (a.zp ? 2 : 1);
+  const size_t fixed = 256 + (size_t)kCW * rows_per_cta * 8 * 4;
+  const size_t cap = (size_t)max_dynamic_smem();
+  if (fixed + 2 * stage_bytes > cap) return NPB_ERR_UNSUPPORTED;
+  int stages = (int)((cap - fixed) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  a.stages = stages;
+  const size_t smem = fixed + (size_t)stages * stage_bytes;
+  auto kern = a.zp ? q4_gemv_ring8_kernel<T, true> : q4_gemv_ring8_kernel<T, false>;
+  int per_sm = 0;
+  if (int rc = blocks_per_sm(reinterpret_cast<const void*>(kern), kThreads, smem, &per_sm)) return rc;
+  if (per_sm < 1) return NPB_ERR_UNSUPPORTED;
+  a.wait_ns = wait_limit_ns();
+  kern<<<grid, kThreads, smem, st>>>(a);
+  NPB_LAUNCH_CHECK();
+  return NPB_OK;
+}
+
 }  // namespace
 
-// Reads and clears this kernel's give-up record (1: producer, 2: a consumer); merged into
+// Reads and clears this kernel's give-up record (1 / 3: a producer, 2 / 4: a consumer); merged into
 // npb_gemm_device_status.
 int q_gemv_ring_device_status(int* host_out) {
   int v = 0;
@@ -343,12 +552,13 @@ int q_gemv_ring_device_status(int* host_out) {
 }
 
 // Returns NPB_ERR_UNSUPPORTED for shapes this kernel does not take (the caller then uses the
-// register-fed tensor-core GEMV): 1-2 rows, 4-bit codes, K a multiple of 4096, power-of-two
+// register-fed tensor-core GEMV): 1-2 rows (3-8 rows: K = 4096), 4-bit codes, K a multiple of 4096, power-of-two
 // groups of at least 32, rows and scale rows that start on 16-byte boundaries.
 int q4_gemv_ring(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t N, int64_t K,
                  const float* bias, void* y, cudaStream_t st) {
   if (w->nbits != 4 || (x_dtype != NPB_BF16 && x_dtype != NPB_F16)) return NPB_ERR_UNSUPPORTED;
-  if (M < 1 || M > 2 || K % 4096 != 0 || K > 8192 || N < 8 || N >= (int64_t)1 << 30) return NPB_ERR_UNSUPPORTED;
+  if (M < 1 || M > 8 || K % 4096 != 0 || K > 8192 || N < 8 || N >= (int64_t)1 << 30) return NPB_ERR_UNSUPPORTED;
+  if (M > 2 && (K != 4096 || N < 16)) return NPB_ERR_UNSUPPORTED;   // the 3-8-row form keeps one 256-wide slice per warp
   int gs_shift = 0;
   while ((1 << gs_shift) < w->group_size) ++gs_shift;
   if ((1 << gs_shift) != w->group_size || w->group_size < 32 || w->group_size > 128) return NPB_ERR_UNSUPPORTED;
@@ -366,6 +576,7 @@ int q4_gemv_ring(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, i
   a.y = y;
   a.M = (int)M; a.N = (int)N; a.K = (int)K;
   a.gs_shift = gs_shift;
+  if (M > 2) return x_dtype == NPB_BF16 ? launch_ring8<__nv_bfloat16>(a, st) : launch_ring8<__half>(a, st);
   const int pairs = (int)(K / 4096);   // 256-wide step pairs of a consumer warp's K slice
   if (pairs > 2) return NPB_ERR_UNSUPPORTED;   // the activation operand of the slice must fit the registers
 #define NPB_RING(TT, MR_, P_) launch_ring<TT, MR_, P_>(a, st)

@@ -456,8 +456,8 @@ int q_gemv(const npb_q_weight* w, const void* x, int x_dtype, int64_t M, int64_t
   a.x = x;
   a.y = y;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.group_size = w->group_size;
-  if (M <= 2) {
-    // 1-2 rows: the weight streamed through a shared-memory ring by bulk async copies
+  {
+    // the weight streamed through a shared-memory ring by bulk async copies (it declines what it does not take)
     const int rc = q4_gemv_ring(w, x, x_dtype, M, N, K, bias, y, st);
     if (rc != NPB_ERR_UNSUPPORTED) return rc;
   }

@@ -157,8 +157,8 @@ def test_vq_gemv_rejects_too_many_rows():
 
 @pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("rows", [1, 2, 8])
-@pytest.mark.parametrize("shape", [(320, 1024), (67, 4096), (40, 192)])
+@pytest.mark.parametrize("rows", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("shape", [(320, 1024), (67, 4096), (40, 192), (100, 512), (2500, 2048)])
 def test_q_gemv_matches_oracle(asym, gs, dtype, rows, shape):
     N, K = shape
     if K % gs:
@@ -174,12 +174,13 @@ def test_q_gemv_matches_oracle(asym, gs, dtype, rows, shape):
 
 @pytest.mark.parametrize("asym,gs", [(False, 32), (True, 64), (True, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("rows", [1, 2])
-@pytest.mark.parametrize("shape", [(67, 4096), (1192, 4096), (200, 8192), (2411, 4096)])
+@pytest.mark.parametrize("rows", [1, 2, 3, 6, 8])
+@pytest.mark.parametrize("shape", [(67, 4096), (1192, 4096), (200, 8192), (2411, 4096), (16, 4096), (5000, 4096)])
 def test_q_gemv_ring_shapes(asym, gs, dtype, rows, shape):
-    """K a multiple of 4096 and 1-2 rows take the bulk-copy ring GEMV: row counts that are not
-    multiples of 8 (the last ring stage re-reads the last row), several stages per CTA, two step
-    pairs per warp (K = 8192)."""
+    """K a multiple of 4096 takes the bulk-copy ring GEMV (1-2 rows; 3-8 rows at K = 4096, sixteen
+    weight rows per stage): row counts that are not multiples of 8 / 16 (the last ring stage re-reads
+    the last row), a single stage, several stages per CTA, two step pairs per warp (K = 8192; 3-8
+    rows then take the register-fed kernel)."""
     N, K = shape
     layer = make_q_layer(N, K, group_size=gs, asym=asym, seed=N + gs, bias=True)
     x = make_activations(rows, K, dtype, seed=rows + N)
