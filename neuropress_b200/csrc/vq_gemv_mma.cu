@@ -208,7 +208,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   const bool has_res = a.has_res != 0, has_scale = a.has_scale != 0;
   // Index words of one (row group, slice) item for this lane's two rows; the next item's are
   // requested before the current item's gathers, so their latency is off the critical path.
-  struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; };
+  // The row scales of a row group travel with its first slice, unconverted: converting them where
+  // they are loaded would make the warp wait for the load at the start of every row group.
+  struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; unsigned short s_lo, s_hi; };
   auto fetch = [&](Item& it, int rg_, int sl_) {
     const SegView sv = seg_of(rg_);
     const int nl = (rg_ - sv.group0) * 16 + g, nh = nl + 8;
@@ -222,19 +224,21 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
     } else {
       it.rlo.w[0] = it.rlo.w[1] = it.rhi.w[0] = it.rhi.w[1] = 0u;
     }
+    if (has_scale && sl_ == 0) {
+      const unsigned short* rs = reinterpret_cast<const unsigned short*>(a.row_scale);
+      it.s_lo = __ldg(rs + rl);
+      it.s_hi = __ldg(rs + rh);
+    }
   };
   Item nxt;
   if ((int)blockIdx.x < n_groups) fetch(nxt, blockIdx.x, 0);
   int buf = 0;
   for (int rg = blockIdx.x; rg < n_groups; rg += gridDim.x, buf ^= 1) {
     const SegView sv = seg_of(rg);
-    const int n_lo = (rg - sv.group0) * 16 + g, n_hi = n_lo + 8;
-    // rows past N read row N - 1 (mapped); their results are not stored
-    const int r_lo = n_lo < sv.N ? n_lo : sv.N - 1, r_hi = n_hi < sv.N ? n_hi : sv.N - 1;
     __half2 s_lo = __float2half2_rn(1.f), s_hi = s_lo;
-    if (has_scale) {
-      s_lo = __half2half2(__ldg(a.row_scale + (has_scale ? r_lo : 0)));
-      s_hi = __half2half2(__ldg(a.row_scale + (has_scale ? r_hi : 0)));
+    if (has_scale) {   // loaded with the first slice's index words (nxt holds slice 0 of this row group here)
+      s_lo = __half2half2(__ushort_as_half(nxt.s_lo));
+      s_hi = __half2half2(__ushort_as_half(nxt.s_hi));
     }
     float acc[MT][4];
 #pragma unroll
