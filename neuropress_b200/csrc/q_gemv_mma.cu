@@ -69,7 +69,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_gemv_mma_kernel(MmaArgs a) {
   const int my_blocks = blockIdx.x < n_blocks ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const int total = my_blocks * spw;                            // this warp's flattened step list
 
-  struct Step { uint4 ca, cb; __half2 s, z; };
+  // Scales / zero points stay as loaded (one register per 16-bit load) until they are used: packing
+  // them here would make the warp wait for the loads where they are issued.
+  struct Step { uint4 ca, cb; unsigned short sA, sB, zA, zB; };
+  const unsigned short* scale_u = reinterpret_cast<const unsigned short*>(a.scale);
+  const unsigned short* zp_u = reinterpret_cast<const unsigned short*>(a.zp);
   auto load_step = [&](Step& st, int q) {
     const int rb = blockIdx.x + (q / spw) * gridDim.x;
     const int kb = warp + (q % spw) * WARPS;
@@ -78,11 +82,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_gemv_mma_kernel(MmaArgs a) {
     st.ca = __ldg(reinterpret_cast<const uint4*>(a.codes + (size_t)rA * (K / 2) + kb * 64 + t * 16));
     st.cb = __ldg(reinterpret_cast<const uint4*>(a.codes + (size_t)rB * (K / 2) + kb * 64 + t * 16));
     const int grp = (kb * 128 + t * 32) / gs;
-    st.s = __halves2half2(__ldg(a.scale + (size_t)rA * groups + grp),
-                          __ldg(a.scale + (size_t)rB * groups + grp));
-    st.z = a.zp ? __halves2half2(__ldg(a.zp + (size_t)rA * groups + grp),
-                                 __ldg(a.zp + (size_t)rB * groups + grp))
-                : __float2half2_rn(8.f);
+    st.sA = __ldg(scale_u + (size_t)rA * groups + grp);
+    st.sB = __ldg(scale_u + (size_t)rB * groups + grp);
+    st.zA = st.zB = 0x4800;   // 8.0
+    if (a.zp) {
+      st.zA = __ldg(zp_u + (size_t)rA * groups + grp);
+      st.zB = __ldg(zp_u + (size_t)rB * groups + grp);
+    }
   };
 
   // The first kPrefetch steps are requested before the activations are staged.
@@ -172,8 +178,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_gemv_mma_kernel(MmaArgs a) {
         }
       }
       // D columns 2t, 2t+1 = this lane's own 32-block against activation rows (2mp, 2mp+1)
-      const float2 sc = __half22float2(cur.s), zc = __half22float2(cur.z);
-      const float ca = kOffset + zc.x, cb = kOffset + zc.y;
+      const float2 sc = make_float2(__half2float(__ushort_as_half(cur.sA)), __half2float(__ushort_as_half(cur.sB)));
+      const float ca = kOffset + __half2float(__ushort_as_half(cur.zA));
+      const float cb = kOffset + __half2float(__ushort_as_half(cur.zB));
 #pragma unroll
       for (int mp = 0; mp < MP; ++mp) {
         const float x0 = xsum[(2 * mp) * (K / 32) + kb * 4 + t];

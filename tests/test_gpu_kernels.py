@@ -192,6 +192,20 @@ def test_q_gemv_ring_shapes(asym, gs, dtype, rows, shape):
     assert _cabi.gemm_device_status() == 0
 
 
+@pytest.mark.parametrize("asym", [False, True])
+@pytest.mark.parametrize("rows", [1, 2, 3, 8])
+def test_q_gemv_group_size_that_is_not_a_power_of_two(asym, rows):
+    """Groups of 96 (K = 1536): the ring and full-column kernels decline (they shift by the group
+    size), the block-diagonal tensor-core kernel takes every row count."""
+    N, K, gs = 200, 1536, 96
+    layer = make_q_layer(N, K, group_size=gs, asym=asym, seed=N + gs, bias=True)
+    x = make_activations(rows, K, torch.bfloat16, seed=rows)
+    y = kernels.q_gemv(x.to(DEV), layer.codes.to(DEV), layer.scale.to(DEV), 4, gs,
+                       None if layer.zero_point is None else layer.zero_point.to(DEV), layer.bias.to(DEV))
+    ref = oracle.q_forward_f64(x, layer.codes, layer.scale, 4, gs, layer.zero_point, layer.bias)
+    assert_output_close(y, ref, torch.bfloat16)
+
+
 # ------------------------------------------------------------------------- LUT gather ---
 @pytest.mark.parametrize("bits,nc", [(4, 16), (8, 256), (10, 1000), (12, 4096), (16, 5000)])
 @pytest.mark.parametrize("shape", [(37, 96, 1), (256, 512, 3), (100, 40, 16)])
