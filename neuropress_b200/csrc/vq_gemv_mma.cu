@@ -141,6 +141,49 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   // costs a bank-conflicted LDS instead of one L1 tag lookup per lane (1 per clock per SM)
   const uint4* cbs = rtab + (a.has_res ? a.res_num_centroids * 8 : 0);
 
+  const int n_groups = a.n_segs > 1 ? a.total_groups : (a.N + 15) / 16;
+  const int chunks_per_row = a.G >> 3;  // 8-index chunks per W row
+  // Weight that owns row group rg: its index stream, codebook, row count and first group.
+  struct SegView { const uint8_t* packed; const __half* centroids; const float* bias; int N, group0, col0; };
+  auto seg_of = [&](int rg_) -> SegView {
+    if (a.n_segs <= 1) return SegView{a.packed, a.centroids, a.bias, a.N, 0, 0};
+    int s_ = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxSegs; ++i)
+      if (i < a.n_segs && rg_ >= a.seg[i].group0) s_ = i;
+    return SegView{a.seg[s_].packed, a.seg[s_].centroids, a.seg[s_].bias, a.seg[s_].N, a.seg[s_].group0,
+                   a.seg[s_].col0};
+  };
+  const bool has_res = a.has_res != 0, has_scale = a.has_scale != 0;
+  // Index words of one (row group, slice) item for this lane's two rows; the next item's are
+  // requested before the current item's gathers, so their latency is off the critical path.
+  // The row scales of a row group travel with its first slice, unconverted: converting them where
+  // they are loaded would make the warp wait for the load at the start of every row group.
+  struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; unsigned short s_lo, s_hi; };
+  auto fetch = [&](Item& it, int rg_, int sl_) {
+    const SegView sv = seg_of(rg_);
+    const int nl = (rg_ - sv.group0) * 16 + g, nh = nl + 8;
+    const int rl = nl < sv.N ? nl : sv.N - 1, rh = nh < sv.N ? nh : sv.N - 1;  // rows past N: row N-1
+    const int c0 = (warp * a.slices_per_warp + sl_) * 4 + t;               // chunk of 8 indices in the row
+    it.lo = load_raw<BITS>(sv.packed, (int64_t)rl * chunks_per_row + c0);
+    it.hi = load_raw<BITS>(sv.packed, (int64_t)rh * chunks_per_row + c0);
+    if (has_res) {
+      it.rlo = load_raw<8>(a.res_packed, (int64_t)rl * chunks_per_row + c0);
+      it.rhi = load_raw<8>(a.res_packed, (int64_t)rh * chunks_per_row + c0);
+    } else {
+      it.rlo.w[0] = it.rlo.w[1] = it.rhi.w[0] = it.rhi.w[1] = 0u;
+    }
+    if (has_scale && sl_ == 0) {
+      const unsigned short* rs = reinterpret_cast<const unsigned short*>(a.row_scale);
+      it.s_lo = __ldg(rs + rl);
+      it.s_hi = __ldg(rs + rh);
+    }
+  };
+  // The first item's index words are requested before the activations are staged: their latency
+  // runs under the staging instead of after it.
+  Item nxt;
+  if ((int)blockIdx.x < n_groups) fetch(nxt, blockIdx.x, 0);
+
   // ---- stage activations (zero rows past M) and the replicated residual table ----
   {
     const T* x = static_cast<const T*>(a.x);
@@ -192,46 +235,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   }
   __syncthreads();
 
-  const int n_groups = a.n_segs > 1 ? a.total_groups : (a.N + 15) / 16;
-  const int chunks_per_row = a.G >> 3;  // 8-index chunks per W row
-  // Weight that owns row group rg: its index stream, codebook, row count and first group.
-  struct SegView { const uint8_t* packed; const __half* centroids; const float* bias; int N, group0, col0; };
-  auto seg_of = [&](int rg_) -> SegView {
-    if (a.n_segs <= 1) return SegView{a.packed, a.centroids, a.bias, a.N, 0, 0};
-    int s_ = 0;
-#pragma unroll
-    for (int i = 1; i < kMaxSegs; ++i)
-      if (i < a.n_segs && rg_ >= a.seg[i].group0) s_ = i;
-    return SegView{a.seg[s_].packed, a.seg[s_].centroids, a.seg[s_].bias, a.seg[s_].N, a.seg[s_].group0,
-                   a.seg[s_].col0};
-  };
-  const bool has_res = a.has_res != 0, has_scale = a.has_scale != 0;
-  // Index words of one (row group, slice) item for this lane's two rows; the next item's are
-  // requested before the current item's gathers, so their latency is off the critical path.
-  // The row scales of a row group travel with its first slice, unconverted: converting them where
-  // they are loaded would make the warp wait for the load at the start of every row group.
-  struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; unsigned short s_lo, s_hi; };
-  auto fetch = [&](Item& it, int rg_, int sl_) {
-    const SegView sv = seg_of(rg_);
-    const int nl = (rg_ - sv.group0) * 16 + g, nh = nl + 8;
-    const int rl = nl < sv.N ? nl : sv.N - 1, rh = nh < sv.N ? nh : sv.N - 1;  // rows past N: row N-1
-    const int c0 = (warp * a.slices_per_warp + sl_) * 4 + t;               // chunk of 8 indices in the row
-    it.lo = load_raw<BITS>(sv.packed, (int64_t)rl * chunks_per_row + c0);
-    it.hi = load_raw<BITS>(sv.packed, (int64_t)rh * chunks_per_row + c0);
-    if (has_res) {
-      it.rlo = load_raw<8>(a.res_packed, (int64_t)rl * chunks_per_row + c0);
-      it.rhi = load_raw<8>(a.res_packed, (int64_t)rh * chunks_per_row + c0);
-    } else {
-      it.rlo.w[0] = it.rlo.w[1] = it.rhi.w[0] = it.rhi.w[1] = 0u;
-    }
-    if (has_scale && sl_ == 0) {
-      const unsigned short* rs = reinterpret_cast<const unsigned short*>(a.row_scale);
-      it.s_lo = __ldg(rs + rl);
-      it.s_hi = __ldg(rs + rh);
-    }
-  };
-  Item nxt;
-  if ((int)blockIdx.x < n_groups) fetch(nxt, blockIdx.x, 0);
   int buf = 0;
   for (int rg = blockIdx.x; rg < n_groups; rg += gridDim.x, buf ^= 1) {
     const SegView sv = seg_of(rg);
