@@ -56,7 +56,7 @@ constexpr int UMMA_K = 16;
 constexpr int kAStageBytes = BM * BK * 2;
 constexpr int kDecodeWarps = 16;
 constexpr int kMaxGroups = kDecodeWarps;            // decode groups = ring stages (1, 2 or 4 warps each)
-constexpr int kThreads = 192 + 32 * kDecodeWarps;   // 704
+constexpr int kThreads = 192 + 32 * kDecodeWarps + 32;   // 736: the last warp is the second mma issuer
 constexpr int kBarrierBytes = 1024;
 constexpr int kResTableBytes = 256 * 16;
 
@@ -89,6 +89,7 @@ struct FusedParams {
   int has_res, has_scale;
   int clamp;                     // copy form: indices can exceed the codebook (NC < 2^bits) or take an offset
   int M, N, K, BN, tiles_m, tiles_n, groups, warps_per_group;
+  int dual;                      // two mma-issuing threads, one accumulator each (narrow tiles)
   int n_segs, ld_y;              // segments of a grouped launch (1: the plain call) and the row pitch of y
   Seg seg[kMaxSegs];
 };
@@ -284,9 +285,15 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
   const int num_kb = p.K / BK;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int acc_cols = MT * BN;
-  const int nbuf = (2 * acc_cols <= 512) ? 2 : 1;
+  // Narrow tiles are bound by the rate at which ONE thread issues tcgen05.mma (four K = 16 instructions
+  // and a commit per k block, ~70 cycles each).  In the dual form two threads of different warps issue
+  // the even and the odd k blocks into accumulators of their own, which the epilogue adds; the stage
+  // count is even, so a stage always belongs to the same issuer and each of its barriers sees one
+  // waiter on consecutive phases.
+  const int nacc = p.dual ? 2 : 1;
+  const int nbuf = (2 * nacc * acc_cols <= 512) ? 2 : 1;
   int tmem_cols = 32;
-  while (tmem_cols < nbuf * acc_cols) tmem_cols <<= 1;
+  while (tmem_cols < nbuf * nacc * acc_cols) tmem_cols <<= 1;
   const uint32_t idesc = umma_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, BM, BN);
 
   if (threadIdx.x == 0) {
@@ -297,7 +304,7 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_full[b], nacc);
       mbar_init(&tmem_empty[b], 4);
     }
     fence_barrier_init();
@@ -338,10 +345,13 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
         }
       }
     }
-  } else if (warp == 1) {
-    // ================= MMA issuer =================
+  } else if (warp == 1 || (warp == kThreads / 32 - 1 && p.dual)) {
+    // ================= MMA issuer(s): issuer j takes the k blocks j, j + nacc, ... of every tile =================
     if (lane == 0) {
-      int s = 0;
+      const int j0 = warp == 1 ? 0 : 1;
+      // This issuer's items are j0, j0 + nacc, ... of the CTA's item list (in the dual form K / 64 is
+      // even, so the list of every tile continues the stride): stage and phase advance without a division.
+      int s = j0;
       uint32_t ph = 0;
       int it = 0;
       bool ok = true;
@@ -353,8 +363,8 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
           break;
         }
         tc_fence_after();
-        const uint32_t acc = tmem_base + buf * acc_cols;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const uint32_t acc = tmem_base + (buf * nacc + j0) * acc_cols;
+        for (int kb = j0; kb < num_kb; kb += nacc) {
           if (!mbar_wait_bounded(&full_bar[s], ph, abort_flag, p.wait_ns)) {
             atomicExch(&g_vq_fused_status, 2);
             ok = false;
@@ -369,10 +379,11 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
             const uint64_t adesc = umma_desc_sw128(st + mt * kAStageBytes);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
-              umma_f16(acc + mt * BN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              umma_f16(acc + mt * BN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > j0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);
-          if (++s == G) { s = 0; ph ^= 1; }
+          s += nacc;
+          if (s >= G) { s -= G; ph ^= 1; }
         }
         if (ok) umma_commit(&tmem_full[buf]);
       }
@@ -394,7 +405,7 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
         break;
       }
       tc_fence_after();
-      const uint32_t acc = tmem_base + buf * acc_cols + ((uint32_t)(quad * 32) << 16);
+      const uint32_t acc = tmem_base + buf * nacc * acc_cols + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
       for (int mt = 0; mt < MT; ++mt) {
         if ((tm * MT + mt) * BM >= p.M) break;  // whole sub-tile past M: skipped by all lanes together
@@ -404,6 +415,13 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
           uint32_t v[16];
           tmem_ld_32x32_x16(acc + mt * BN + c * 16, v);
           tmem_ld_wait();
+          if (p.dual) {   // the odd k blocks' accumulator
+            uint32_t w[16];
+            tmem_ld_32x32_x16(acc + acc_cols + mt * BN + c * 16, w);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(w[e]));
+          }
           const int n0 = seg_n0 + c * 16;
           if (m < p.M && n0 < sg.N) {
             T* dst = y + (int64_t)m * p.ld_y + sg.col0 + n0;
@@ -440,7 +458,7 @@ vq_gemm_fused_kernel(const __grid_constant__ CUtensorMap tmap_a, const FusedPara
     const int dw = warp - 6;
     const int wpg = p.warps_per_group;        // 1, 2 or 4 warps share a stage's BN rows
     const int grp = dw / wpg, part = dw - grp * wpg;
-    if (grp < G) {
+    if (dw < kDecodeWarps && grp < G) {
       const int rows_per_warp = BN / wpg;
       const int row0 = part * rows_per_warp;
       const int my_tiles = (int)blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -593,6 +611,11 @@ int launch(const void* x, FusedParams p, cudaStream_t st) {
   int groups = (cap - kBarrierBytes - kResTableBytes - 1024) / stage_bytes;
   if (groups > kDecodeWarps / wpg) groups = kDecodeWarps / wpg;
   if (groups < 2) return NPB_ERR_UNSUPPORTED;
+  // Dual issue for tiles of up to 32 columns with one row tile: from 64 columns on a k block's gathers
+  // take as long as its mmas take to issue, and a second issuer only adds contention (8192 x 8192 at
+  // 32 rows: 56 -> 63 us; 1024 x 8192: 45 -> 33 us).
+  p.dual = (MT == 1 && p.BN <= 32 && (p.K / BK) % 2 == 0 && groups >= 4) ? 1 : 0;
+  if (p.dual) groups &= ~1;
   p.groups = groups;
   const int smem = kBarrierBytes + kResTableBytes + 1024 + groups * stage_bytes;
   static int configured[64] = {0};
