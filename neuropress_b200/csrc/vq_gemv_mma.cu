@@ -160,47 +160,29 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   // The row scales of a row group travel with its first slice, unconverted: converting them where
   // they are loaded would make the warp wait for the load at the start of every row group.
   struct Item { RawIdx<BITS> lo, hi; RawIdx<8> rlo, rhi; unsigned short s_lo, s_hi; };
-  // The CTA's row groups.  One weight: a contiguous range of ROWS per CTA (N / grid rows, the first
-  // N % grid CTAs one more), walked in groups of 16 of which the last may be partial -- the gathers of
-  // rows past the range are not issued, so every SM gets the same number of gathers (with whole groups
-  // dealt round-robin, 896 groups on 148 SMs leave 7 for some and 6 for most).  Several weights: whole
-  // groups round-robin over the stacked groups, rows past a weight's end not gathered either.
-  struct Grp { SegView sv; int row0, row_end; };   // rows [row0, row0 + 16) of sv, valid below row_end
-  const bool contiguous = a.n_segs <= 1;
-  const int row_base = a.N / (int)gridDim.x, row_rem = a.N % (int)gridDim.x;
-  const int cta_row0 = (int)blockIdx.x * row_base + ((int)blockIdx.x < row_rem ? (int)blockIdx.x : row_rem);
-  const int cta_row1 = cta_row0 + row_base + ((int)blockIdx.x < row_rem ? 1 : 0);
-  const int n_local = contiguous ? (cta_row1 - cta_row0 + 15) / 16
-                                 : ((int)blockIdx.x < n_groups ? (n_groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0);
-  auto group_at = [&](int li) -> Grp {
-    if (contiguous) return Grp{seg_of(0), cta_row0 + 16 * li, cta_row1};
-    const int rg_ = (int)blockIdx.x + li * (int)gridDim.x;
+  auto fetch = [&](Item& it, int rg_, int sl_) {
     const SegView sv = seg_of(rg_);
-    return Grp{sv, (rg_ - sv.group0) * 16, sv.N};
-  };
-  auto fetch = [&](Item& it, const Grp& gp, int sl_) {
-    const int rl = gp.row0 + g, rh = rl + 8;
-    const bool vl = rl < gp.row_end, vh = rh < gp.row_end;
+    const int nl = (rg_ - sv.group0) * 16 + g, nh = nl + 8;
+    const int rl = nl < sv.N ? nl : sv.N - 1, rh = nh < sv.N ? nh : sv.N - 1;  // rows past N: row N-1
     const int c0 = (warp * a.slices_per_warp + sl_) * 4 + t;               // chunk of 8 indices in the row
-    it.lo = RawIdx<BITS>{};
-    it.hi = RawIdx<BITS>{};
-    it.rlo.w[0] = it.rlo.w[1] = it.rhi.w[0] = it.rhi.w[1] = 0u;
-    if (vl) it.lo = load_raw<BITS>(gp.sv.packed, (int64_t)rl * chunks_per_row + c0);
-    if (vh) it.hi = load_raw<BITS>(gp.sv.packed, (int64_t)rh * chunks_per_row + c0);
+    it.lo = load_raw<BITS>(sv.packed, (int64_t)rl * chunks_per_row + c0);
+    it.hi = load_raw<BITS>(sv.packed, (int64_t)rh * chunks_per_row + c0);
     if (has_res) {
-      if (vl) it.rlo = load_raw<8>(a.res_packed, (int64_t)rl * chunks_per_row + c0);
-      if (vh) it.rhi = load_raw<8>(a.res_packed, (int64_t)rh * chunks_per_row + c0);
+      it.rlo = load_raw<8>(a.res_packed, (int64_t)rl * chunks_per_row + c0);
+      it.rhi = load_raw<8>(a.res_packed, (int64_t)rh * chunks_per_row + c0);
+    } else {
+      it.rlo.w[0] = it.rlo.w[1] = it.rhi.w[0] = it.rhi.w[1] = 0u;
     }
     if (has_scale && sl_ == 0) {
       const unsigned short* rs = reinterpret_cast<const unsigned short*>(a.row_scale);
-      it.s_lo = vl ? __ldg(rs + rl) : (unsigned short)0;
-      it.s_hi = vh ? __ldg(rs + rh) : (unsigned short)0;
+      it.s_lo = __ldg(rs + rl);
+      it.s_hi = __ldg(rs + rh);
     }
   };
   // The first item's index words are requested before the activations are staged: their latency
   // runs under the staging instead of after it.
   Item nxt;
-  if (n_local > 0) fetch(nxt, group_at(0), 0);
+  if ((int)blockIdx.x < n_groups) fetch(nxt, blockIdx.x, 0);
 
   // ---- stage activations (zero rows past M) and the replicated residual table ----
   {
@@ -254,10 +236,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
   __syncthreads();
 
   int buf = 0;
-  for (int li = 0; li < n_local; ++li, buf ^= 1) {
-    const Grp gp = group_at(li);
-    const SegView sv = gp.sv;
-    const bool v_lo = gp.row0 + g < gp.row_end, v_hi = gp.row0 + 8 + g < gp.row_end;
+  for (int rg = blockIdx.x; rg < n_groups; rg += gridDim.x, buf ^= 1) {
+    const SegView sv = seg_of(rg);
     __half2 s_lo = __float2half2_rn(1.f), s_hi = s_lo;
     if (has_scale) {   // loaded with the first slice's index words (nxt holds slice 0 of this row group here)
       s_lo = __half2half2(__ushort_as_half(nxt.s_lo));
@@ -272,8 +252,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
     for (int sl = 0; sl < a.slices_per_warp; ++sl) {
       const int slice = warp * a.slices_per_warp + sl;  // 32 vectors = 256 k
       const Item cur = nxt;
-      if (sl + 1 < a.slices_per_warp) fetch(nxt, gp, sl + 1);
-      else if (li + 1 < n_local) fetch(nxt, group_at(li + 1), 0);
+      if (sl + 1 < a.slices_per_warp) fetch(nxt, rg, sl + 1);
+      else if (rg + (int)gridDim.x < n_groups) fetch(nxt, rg + gridDim.x, 0);
       uint32_t idx_lo[8], idx_hi[8], rdx_lo[8], rdx_hi[8];
       expand<BITS>(cur.lo, idx_lo);
       expand<BITS>(cur.hi, idx_hi);
@@ -290,14 +270,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
         Half8 c_lo[4], c_hi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          c_lo[j] = Half8{};   // rows past the range: no gather (their outputs are not stored)
-          c_hi[j] = Half8{};
           if constexpr (CBS) {
-            if (v_lo) c_lo[j] = *reinterpret_cast<const Half8*>(cbs + idx_lo[4 * h + j]);
-            if (v_hi) c_hi[j] = *reinterpret_cast<const Half8*>(cbs + idx_hi[4 * h + j]);
+            c_lo[j] = *reinterpret_cast<const Half8*>(cbs + idx_lo[4 * h + j]);
+            c_hi[j] = *reinterpret_cast<const Half8*>(cbs + idx_hi[4 * h + j]);
           } else {
-            if (v_lo) c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_lo[4 * h + j]);
-            if (v_hi) c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_hi[4 * h + j]);
+            c_lo[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_lo[4 * h + j]);
+            c_hi[j] = ldg_vec(reinterpret_cast<const Half8*>(sv.centroids) + idx_hi[4 * h + j]);
           }
         }
 #pragma unroll
@@ -351,9 +329,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) vq_gemv_mma_kernel(MmaVqArgs a)
 #pragma unroll 4
       for (int w = 0; w < WARPS; ++w) sum += p[(size_t)w * MT * 128];
       const int mt = i >> 7, ln = (i >> 2) & 31, c = i & 3;
-      const int n = gp.row0 + (ln >> 2) + 8 * (c >> 1);
+      const int n = (rg - sv.group0) * 16 + (ln >> 2) + 8 * (c >> 1);
       const int m = mt * 8 + 2 * (ln & 3) + (c & 1);
-      if (n < gp.row_end && m < a.M) {
+      if (n < sv.N && m < a.M) {
         if (sv.bias) sum += __ldg(sv.bias + n);
         if (a.sink.peer_out == nullptr)
           static_cast<T*>(a.y)[(size_t)m * a.ld_y + sv.col0 + n] = from_f32<T>(sum);
